@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE expert-FFN decode path (BASELINE.json configs[1]).
+
+One "step" is one decode pass of one MoE layer over M tokens (default M = 1):
+router -> top-k -> batch union -> int4 x int8 gate/up + SwiGLU -> down ->
+routing-weighted combine, all experts resident in HBM.
+
+    python bench.py --gpus 1 --steps K --warmup W          # this backend
+    python bench.py --impl reference --steps K --warmup W  # the reference's CPU int4 path (oracle port)
+
+Prints ONE JSON line (rank 0).  Timing: CUDA events on the stream the kernels
+are launched on, L2 flushed (256 MiB memset, untimed) before every step, max
+over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+# BASELINE.json configs[1]: single decode layer, all experts resident
+CFG = dict(hidden=6144, inter=2048, n_experts=256, k=8, n_shared=1, gs=32, norm_topk=True, routed_scale=2.5)
+METRIC = "moe_expert_ffn_decode_tok_s"
+UNIT = "tok/s"
+N_TOKENS = 64           # distinct synthetic tokens cycled through the steps
+FLUSH_BYTES = 256 << 20  # > 126 MB L2
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up + one down GEMV launch
+# (ncu capture, see profiles/); None until a capture has been taken.
+NCU_GEMV_TRAFFIC_BYTES_PER_STEP = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def algorithmic_bytes(n_union: int, m: int):
+    """Bytes one step must move: (|U| + shared) experts, router weights, x in and out."""
+    from peregrine_b200.synth import expert_bytes
+
+    c = CFG
+    we = expert_bytes(c["hidden"], c["inter"], c["gs"])
+    gu = we * 2 // 3
+    dn = we // 3
+    ne = n_union + c["n_shared"]
+    total = ne * we + c["n_experts"] * c["hidden"] * 4 + 2 * m * c["hidden"] * 4
+    return total, ne * gu, ne * dn
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.01)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unsampled"]}
+        return {"sm_mhz": int(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def host_layer(seed: int, distinct: int):
+    from peregrine_b200.synth import synth_layer
+
+    c = CFG
+    return synth_layer(seed, c["hidden"], c["inter"], c["n_experts"], c["k"], c["gs"], shared=True,
+                       norm_topk=c["norm_topk"], routed_scale=c["routed_scale"], zipf=True,
+                       distinct_experts=distinct)
+
+
+def cpu_pass(layer, xs, threads: int, budget_s: float, max_tokens: int = 4096):
+    """Times the oracle's layer forward (the reference's CPU int4 path restated in C) one
+    token at a time until `budget_s` of CPU work has been spent.  Returns tok/s, tokens."""
+    import oracle as po
+
+    def ow(m):
+        return po.Weight(m.q, m.scale, 4, m.gs, m.i_n, m.o_n)
+
+    experts = [(ow(e.gate), ow(e.up), ow(e.down)) for e in layer.experts]
+    shared = (ow(layer.shared.gate), ow(layer.shared.up), ow(layer.shared.down))
+    c = CFG
+
+    def one(x):
+        return po.moe_forward(x, layer.router_w, layer.router_bias, experts, shared, x.shape[0], c["hidden"], c["k"],
+                              c["norm_topk"], c["routed_scale"], threads=threads)
+
+    one(xs[0:1])  # warm-up (page in the weights touched, spin up the pool)
+    n, spent, times = 0, 0.0, []
+    while spent < budget_s and n < max_tokens:
+        x = xs[n % len(xs)][None, :]
+        t0 = time.perf_counter()
+        one(x)
+        dt = time.perf_counter() - t0
+        times.append(dt)
+        spent += dt
+        n += 1
+    med = float(np.median(times))
+    return 1.0 / med, n, med
+
+
+def run_reference(args, rank: int, world: int):
+    """The reference's own CPU implementation of the path (oracle port), all host threads."""
+    if rank != 0:
+        return
+    import oracle as po
+    from peregrine_b200.synth import synth_tokens
+
+    po.build()
+    threads = os.cpu_count() or 1
+    layer = host_layer(seed=1, distinct=32)
+    xs = synth_tokens(2, N_TOKENS, CFG["hidden"])
+    # each step = one token; warm-up + steps bounded so the run ends within minutes
+    # a step is one decode token; the sample is bounded to ~60 s of CPU work
+    tok_s, n, med = cpu_pass(layer, xs, threads, budget_s=60.0, max_tokens=args.steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": n,
+        "warmup": 1, "ms_per_step": med * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 x int8 -> int32 -> f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: one MoE decode layer, hidden 6144, 256 experts top-8 + 1 shared, "
+                               "moe_inter 2048, int4 group-32, M=1, Zipf(1.1) selection bias", "m": 1},
+        "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": threads, "kind": "port",
+                         "simd": "avx2" if po.simd_tier() == 1 else "scalar",
+                         "sample": f"{n} decode tokens, median per-token time; 32 distinct expert blobs on the host"},
+        "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank: int, local_rank: int, world: int):
+    import torch
+
+    from peregrine_b200 import cuda
+    from peregrine_b200.resident import upload_expert
+    from peregrine_b200.synth import synth_expert, synth_tokens, zipf_bias
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # noqa: F811
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    c = CFG
+    m = args.m
+    dev = local_rank
+    torch.cuda.set_device(dev)
+    if cuda.init([dev]) < 1:
+        raise RuntimeError("bench: the CUDA backend could not initialise its device (no CPU fallback exists)")
+    # ---- resident layer: every expert generated and uploaded separately
+    rng = np.random.default_rng(1234 + rank)
+    router_w = (rng.standard_normal((c["n_experts"], c["hidden"])).astype(np.float32) * np.float32(0.02))
+    bias = zipf_bias(rng, c["n_experts"])
+    ml = cuda.MoeLayer(dev, c["hidden"], c["inter"], c["n_experts"], c["k"], c["norm_topk"], c["routed_scale"],
+                       router_w, bias)
+    t_up = time.time()
+    for e in range(c["n_experts"] + 1):
+        ml.set_expert(e, upload_expert(dev, synth_expert(rng, c["hidden"], c["inter"], c["gs"]), c["hidden"],
+                                       c["inter"]))
+    t_up = time.time() - t_up
+    stream = torch.cuda.ExternalStream(cuda.lib().coli_cuda_stream(dev), device=dev)
+    xs_host = synth_tokens(99 + rank, N_TOKENS * m, c["hidden"]).reshape(N_TOKENS, m, c["hidden"])
+    with torch.cuda.stream(stream):
+        xs = torch.from_numpy(xs_host).cuda(dev)
+        out = torch.empty((m, c["hidden"]), dtype=torch.float32, device=dev)
+        flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    stream.synchronize()
+
+    def step(i, timed_events=None):
+        with torch.cuda.stream(stream):
+            flush.zero_()
+            if timed_events:
+                timed_events[0].record(stream)
+            ml.forward_dev(out.data_ptr(), xs[i % N_TOKENS].data_ptr(), m)
+            if timed_events:
+                timed_events[1].record(stream)
+
+    for i in range(args.warmup):
+        step(i)
+    stream.synchronize()
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    n0 = cuda.kernel_launches()
+    with ClockSampler(dev) as clocks:
+        for i in range(args.steps):
+            step(i, events[i])
+        stream.synchronize()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    launches = cuda.kernel_launches() - n0
+    step_ms = np.array([a.elapsed_time(b) for a, b in events])
+    total_ms = float(step_ms.sum())
+    if dist:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    if cuda.last_device_error(dev) != 0:
+        raise RuntimeError("bench: a kernel reported a device-side error")
+    value = world * m * args.steps / (total_ms * 1e-3)
+
+    # ---- per-kernel times (separate pass over the same steps, events around every launch)
+    prof_steps = min(args.steps, 300)
+    ml.set_profile(True)
+    unions = []
+    for i in range(prof_steps):
+        step(i)
+        unions.append(len(ml.last_routing(m)[3]))
+    stage_ms, ncalls = ml.profile()
+    ml.set_profile(False)
+    n_union = float(np.mean(unions))
+    total_b, gu_b, dn_b = algorithmic_bytes(n_union, m)
+    gemv_ms = (stage_ms["gemv_gateup"] + stage_ms["gemv_down"]) / max(ncalls, 1)
+    gemv_bytes = gu_b + dn_b
+    peak, peak_kind = measured_peaks()
+    achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9 if gemv_ms > 0 else 0.0
+    roofline = {
+        "bound": "hbm", "kernel": "gemv_w4a8_kernel (gate/up + down launches of one step)",
+        "achieved": achieved, "peak": peak, "peak_kind": f"{peak_kind} copy bandwidth", "unit": "GB/s",
+        "frac": achieved / peak, "frac_of_8000": achieved / 8000.0,
+        "traffic": NCU_GEMV_TRAFFIC_BYTES_PER_STEP, "algorithmic_bytes": gemv_bytes,
+        "launch_ms": {"gateup": stage_ms["gemv_gateup"] / max(ncalls, 1), "down": stage_ms["gemv_down"] / max(ncalls, 1)},
+        "gbs": {"gateup": gu_b / (stage_ms["gemv_gateup"] / max(ncalls, 1) * 1e-3) / 1e9 if ncalls else 0,
+                "down": dn_b / (stage_ms["gemv_down"] / max(ncalls, 1) * 1e-3) / 1e9 if ncalls else 0},
+        "stage_ms": {k: v / max(ncalls, 1) for k, v in stage_ms.items()},
+        "kernel_timing": f"separate pass of {prof_steps} steps with CUDA events around every launch",
+    }
+
+    # ---- end to end through the host-pointer call (H2D of x and D2H of the result inside)
+    e2e_steps = min(args.steps, 300)
+    for i in range(3):
+        ml.forward(xs_host[i % N_TOKENS])
+    e2e_t = 0.0
+    for i in range(e2e_steps):
+        with torch.cuda.stream(stream):
+            flush.zero_()
+        stream.synchronize()
+        t0 = time.perf_counter()
+        ml.forward(xs_host[i % N_TOKENS])
+        e2e_t += time.perf_counter() - t0
+    if dist:
+        t = torch.tensor([e2e_t], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_t = float(t.item())
+    e2e = {"value": world * m * e2e_steps / e2e_t, "unit": UNIT, "h2d_bytes_per_step": m * c["hidden"] * 4,
+           "d2h_bytes_per_step": m * c["hidden"] * 4, "steps": e2e_steps,
+           "call": "coli_cuda_moe_layer_forward (host x in, host out back, blocking)"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 x int8 -> int32 -> f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: one MoE decode layer, hidden 6144, 256 experts top-8 + 1 shared, "
+                               "moe_inter 2048, int4 group-32, Zipf(1.1) selection bias, all experts resident",
+                   "m": m, "l2": "flushed before every step (256 MiB memset, untimed)",
+                   "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (one layer copy per GPU)",
+                   "mean_union": n_union, "upload_s": round(t_up, 1)},
+        "hbm_gbs_whole_step": total_b / (total_ms / args.steps * 1e-3) / 1e9,
+        "hbm_frac_of_8000_whole_step": total_b / (total_ms / args.steps * 1e-3) / 1e9 / 8000.0,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        import oracle as po
+
+        po.build()
+        threads = min(os.cpu_count() or 1, 16)  # the reference's default worker count
+        layer = host_layer(seed=1, distinct=32)
+        tok_s, n, med = cpu_pass(layer, xs_host[:, 0, :], threads, budget_s=12.0)
+        line["cpu_baseline"] = {"value": tok_s, "unit": UNIT, "cores": threads, "kind": "port",
+                                "simd": "avx2" if po.simd_tier() == 1 else "scalar",
+                                "sample": f"{n} decode tokens (M=1) of the same layer shape, median per-token time, "
+                                          "32 distinct expert blobs on the host"}
+    ml.free()
+    cuda.shutdown()
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="tokens per step (decode batch)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,223 @@
+/*
+ * C ABI of libcoli_cuda_backend.so — the B200 (sm_100a) MoE expert-FFN backend.
+ *
+ * Part 1 declares, with unchanged names and argument lists, every entry point
+ * of the reference engine's CUDA backend (cuda/backend_cuda.h:29-192), so that
+ * the reference's FFI crate (crates/peregrine-cuda/src/lib.rs:40-145) links
+ * against this library without edits.  Part 2 is additive: grouped-int4
+ * residency and a device-resident MoE layer (router, permutation, experts and
+ * ordered combine with no host round trip).
+ *
+ * Conventions (cuda/backend_cuda.cu:68-72, 614-619): int results are 1 on
+ * success and 0 on failure; nothing throws or aborts; a CUDA failure prints
+ * "[CUDA] <what>: <reason>" on stderr; pointer results are NULL on failure;
+ * statistic getters accept NULL out-pointers.
+ *
+ * Numerics of the int4 paths follow the reference's CPU integer-dot kernels
+ * (crates/peregrine-kernels/src/{quant,idot,matmul}.rs): activations are
+ * quantised to int8 per row, block dots are exact int32, fp32 folding is done
+ * in the reference's order without FMA contraction.
+ */
+#ifndef PEREGRINE_B200_H
+#define PEREGRINE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define COLI_CUDA_MAX_DEVICES 16 /* cuda/backend_cuda.h:21 */
+
+typedef struct ColiCudaTensor ColiCudaTensor; /* cuda/backend_cuda.h:24 */
+typedef struct ColiCudaGraph ColiCudaGraph;   /* cuda/backend_cuda.h:27 */
+
+/* =========================================================================
+ * Part 1 — the reference surface
+ * ========================================================================= */
+
+/* ---- contexts (cuda/backend_cuda.h:30-41; backend_cuda.cu:484-516) ---- */
+/* `devices` are CUDA ordinals; duplicates, out-of-range ordinals and count
+ * outside 1..16 are rejected.  Re-initialising replaces the context set. */
+int coli_cuda_init(const int *devices, int count);
+void coli_cuda_shutdown(void);
+int coli_cuda_device_count(void);       /* contexts this process initialised */
+int coli_cuda_probe_device_count(void); /* devices the driver reports, no init needed */
+int coli_cuda_device_at(int index);     /* ordinal of context `index`, -1 if none */
+int coli_cuda_mem_info(int device, size_t *free_bytes, size_t *total_bytes);
+void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes); /* device < 0: all */
+void coli_cuda_group_stats(uint64_t *calls, uint64_t *experts, uint64_t *rows, double *h2d_ms, double *kernel_ms,
+                           double *d2h_ms); /* times only with COLI_CUDA_PROFILE=1 */
+
+/* ---- residency (cuda/backend_cuda.h:43-52, 132-138; backend_cuda.cu:747-811) ----
+ * fmt: 0 = f32 [O,I]; 1 = int8 [O,I] + scales[O]; 2 = int4, two per byte, stored v+8,
+ * even element in the low nibble + scales[O]; 3 = int2, four per byte, stored v+2 + scales[O].
+ * A call with *tensor already set uploads nothing and reports whether
+ * (fmt, I, O, device) match.  The caller's buffers may be freed on return. */
+int coli_cuda_tensor_upload(ColiCudaTensor **tensor, const void *weights, const float *scales, int fmt, int I, int O,
+                            int device);
+int coli_cuda_tensor_update(ColiCudaTensor *tensor, const void *weights, const float *scales);
+void coli_cuda_tensor_free(ColiCudaTensor *tensor); /* NULL-safe */
+size_t coli_cuda_tensor_bytes(const ColiCudaTensor *tensor);
+int coli_cuda_tensor_device(const ColiCudaTensor *tensor);
+
+/* ---- single matrices (cuda/backend_cuda.h:54-71) ---- */
+/* y[S,O] = x[S,I] W^T with host x/y; uploads W on first use. */
+int coli_cuda_matmul(ColiCudaTensor **tensor, float *y, const float *x, const void *weights, const float *scales,
+                     int fmt, int S, int I, int O, int device);
+/* y = down(silu(gate x) * up x) for S host rows through three resident tensors. */
+int coli_cuda_expert_mlp(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y, const float *x,
+                         int S);
+int coli_cuda_shared_mlp_w4a16(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                               const float *x, int S);
+
+/* ---- the expert group: the GPU lane's hot call (cuda/backend_cuda.h:73-110;
+ * backend_cuda.cu:1035-1259).  Expert c processes rows[c] >= 1 consecutive
+ * host rows of x; y receives sum(rows) rows of width D in the same order.
+ * 1 <= count <= 256; all tensors on one device with gate/up [I,D], down [D,I].
+ * int4 experts (fmt 2, or grouped via Part 2) run the W4A8 integer path;
+ * f32 experts run an fp32 path; the two may be mixed within one call. */
+int coli_cuda_expert_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups, ColiCudaTensor *const *downs,
+                           const int *rows, int count, float *y, const float *x);
+/* Same call with the reference's WMMA tile hint.  This backend has one int4 arm,
+ * so the tile is accepted and ignored; *arm_out (may be NULL) reports the
+ * reference's arm code a caller would expect for the call: 1 when
+ * COLI_CUDA_TC_W4A16 is set and every expert is int4 with rows >= the W4A16
+ * minimum, else 2 for all-int4 groups and 3 otherwise. */
+int coli_cuda_expert_group_tiled(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                 ColiCudaTensor *const *downs, const int *rows, int count, float *y, const float *x,
+                                 int tile_m, int tile_n, int tile_k, int *arm_out);
+/* Same call followed by the CSR combine on the device: out[s,:] (s < s_n) is the
+ * sum, in listed order and starting from zero, of rw[j] * y[j,:] over
+ * j = row_idx[row_ptr[s] .. row_ptr[s+1]).  No atomics: identical bits every run. */
+int coli_cuda_expert_group_reduce(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                  ColiCudaTensor *const *downs, const int *rows, int count, const int *row_ptr,
+                                  const int *row_idx, const float *rw, int s_n, float *out, const float *x);
+
+/* ---- attention (cuda/backend_cuda.h:112-130, 161-176).  Outside the expert-FFN
+ * path: exported so the reference's FFI links; every one reports failure (0),
+ * which the reference's callers treat as "compute this on the CPU lane". ---- */
+int coli_cuda_attention_absorb(ColiCudaTensor *kv_b, float *ctx, const float *q, const float *latent,
+                               const float *rope, int H, int Q, int R, int V, int K, int T, float attention_scale);
+int coli_cuda_attention_absorb_batch(ColiCudaTensor *kv_b, float *ctx, const float *q, const float *latent,
+                                     const float *rope, int S, int H, int Q, int R, int V, int K, int T,
+                                     float attention_scale);
+int coli_cuda_attention_project_batch(ColiCudaTensor *kv_b, ColiCudaTensor *o_proj, float *out, const float *q,
+                                      const float *latent, const float *rope, int S, int H, int Q, int R, int V,
+                                      int K, int T, float attention_scale);
+int coli_cuda_attention_project_batch_dev(ColiCudaTensor *kv_b, ColiCudaTensor *o_proj, float *out,
+                                          const float *q_dev, const float *latent_dev, const float *rope_dev, int S,
+                                          int H, int Q, int R, int V, int K, int T, float scale);
+int coli_cuda_attention_absorb_batch_dev(ColiCudaTensor *kv_b_shard, float *ctx_dev, const float *q_dev,
+                                         const float *latent_dev, const float *rope_dev, int S, int H, int Q, int R,
+                                         int V, int K, int T, float scale);
+int coli_cuda_attention_absorb_kvdev(ColiCudaTensor *kv_b, float *ctx, const float *q, const float *latent_dev,
+                                     const float *rope_dev, int H, int Q, int R, int V, int K, int T, float scale);
+int coli_cuda_attention_project_batch_dev_out(ColiCudaTensor *kv_b, ColiCudaTensor *o_proj, float *out_dev,
+                                              const float *q_dev, const float *latent_dev, const float *rope_dev,
+                                              int S, int H, int Q, int R, int V, int K, int T, float scale);
+
+/* ---- device-pointer primitives on the context's stream (cuda/backend_cuda.h:140-177) ---- */
+float *coli_cuda_pipe_scratch(int device, int slot, size_t bytes); /* 24 grow-only slots */
+void *coli_cuda_pipe_alloc(int device, size_t bytes);
+void coli_cuda_pipe_free(int device, void *p);
+int coli_cuda_pipe_upload(int device, void *dst, const void *src, size_t bytes);
+int coli_cuda_pipe_download(int device, const void *src, void *dst, size_t bytes);
+int coli_cuda_pipe_rmsnorm(int device, float *y_dev, const float *x_dev, const float *w_dev, int S, int D, float eps);
+int coli_cuda_pipe_rmsnorm_s(int device, float *y_dev, const float *x_dev, const float *w_dev, int S, int D,
+                             float eps, int xstride, int ystride);
+int coli_cuda_pipe_rope(int device, float *v_dev, const int *pos_dev, int rows, int stride, int offset, int R,
+                        int heads, float theta);
+int coli_cuda_pipe_rope_base(int device, float *v_dev, int pos_base, int rows, int stride, int offset, int R,
+                             int heads, float theta);
+int coli_cuda_pipe_silu_mul(int device, float *gate_dev, const float *up_dev, size_t n);
+int coli_cuda_pipe_add(int device, float *x_dev, const float *t_dev, size_t n);
+int coli_cuda_pipe_rows_add(int device, float *x_dev, const float *partial_dev, const int *rows_dev, int nrows,
+                            int D);
+int coli_cuda_pipe_gemm(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S);
+int coli_cuda_pipe_copy2d(int device, float *dst, int dpitch, const float *src, int spitch, int width, int height);
+int coli_cuda_pipe_peer_copy(int dst_dev, float *dst, int src_dev, const float *src, size_t bytes);
+int coli_cuda_pipe_sync(int device);
+
+/* ---- stream capture (cuda/backend_cuda.h:179-191) ---- */
+int coli_cuda_graph_begin(int device);
+int coli_cuda_graph_end(int device, ColiCudaGraph **out);
+int coli_cuda_graph_launch(ColiCudaGraph *g);
+void coli_cuda_graph_free(ColiCudaGraph *g);
+/* Counters of the expert-group graph cache (COLI_CUDA_GRAPH=1). */
+void coli_cuda_graph_cache_stats(uint64_t *captures, uint64_t *replays, uint64_t *invalidations,
+                                 uint64_t *uncacheable);
+
+/* =========================================================================
+ * Part 2 — additive entry points (no counterpart in cuda/backend_cuda.h)
+ * ========================================================================= */
+
+/* Grouped int4 residency.  The reference keeps this format on the CPU only
+ * (crates/peregrine-core/src/qt.rs:70-85; crates/peregrine-kernels/src/idot.rs:78-110)
+ * and dequantises it to f32 before upload (crates/peregrine-model/src/gpu.rs:1373-1382).
+ * weights: [O, ceil(I/2)] as fmt 2; scales: [O * ceil(I/gs)], row o group g at
+ * o*ng+g; gs a multiple of 32, at most 256.  The handle works everywhere a
+ * fmt-2 handle does and reports fmt 4. */
+int coli_cuda_tensor_upload_grouped(ColiCudaTensor **tensor, const void *weights, const float *scales, int I, int O,
+                                    int gs, int device);
+
+/* One resident MoE layer: router + E routed experts (+ one shared expert).
+ * Mirrors the arguments of the reference's layer forward
+ * (crates/peregrine-model/src/mlp.rs:46-57, MoeCfg :33-39;
+ * crates/peregrine-model/src/concurrent.rs:1200). */
+typedef struct ColiCudaMoeLayer ColiCudaMoeLayer;
+
+/* router_w: host fp32 [E, D]; router_bias: host fp32 [E] (NULL = zeros). */
+int coli_cuda_moe_layer_create(ColiCudaMoeLayer **layer, int device, int D, int I, int E, int k, int norm_topk,
+                               float routed_scale, const float *router_w, const float *router_bias);
+/* Attach expert `e` (0..E-1 routed, E = the shared expert).  The layer borrows the
+ * tensors; they must outlive it.  All experts must be int4 (fmt 2 or grouped) of
+ * one format, gate/up [I, D], down [D, I]. */
+int coli_cuda_moe_layer_set_expert(ColiCudaMoeLayer *layer, int e, ColiCudaTensor *gate, ColiCudaTensor *up,
+                                   ColiCudaTensor *down);
+void coli_cuda_moe_layer_free(ColiCudaMoeLayer *layer);
+
+/* out[M, D] = MoE(x[M, D]) with device pointers (row strides D), enqueued on the
+ * device's stream with no host synchronisation: route -> batch union -> pair
+ * layout -> quantise -> gate/up + SwiGLU -> quantise -> down -> ordered combine.
+ * Workspace grows (allocates) on the first call at a larger M. */
+int coli_cuda_moe_layer_forward_dev(ColiCudaMoeLayer *layer, float *out_dev, const float *x_dev, int M);
+/* Same with host pointers: copies x in, runs, copies out, blocks until done. */
+int coli_cuda_moe_layer_forward(ColiCudaMoeLayer *layer, float *out, const float *x, int M);
+
+/* Inspection of the last forward (blocking copies to host; any pointer may be NULL).
+ * idx, w: [M*k]; keff: [M]; union_ids: [E] with *n_union entries. */
+int coli_cuda_moe_layer_last_routing(ColiCudaMoeLayer *layer, int M, int *idx, float *w, int *keff, int *union_ids,
+                                     int *n_union);
+/* When enabled, the next forwards also record the per-block int32 accumulators of
+ * every (pair, output, group).  Sizes for M tokens: gate/up taps
+ * [pairs][2][I][ng(D)] and down taps [pairs][D][ng(I)], pairs as reported by
+ * coli_cuda_moe_layer_last_pairs.  For per-row (fmt 2) experts ng is 1 and the tap
+ * is the whole-row accumulator. */
+int coli_cuda_moe_layer_enable_taps(ColiCudaMoeLayer *layer, int enable);
+/* pair_token[p] = token of pair row p, pair_expert[p] = expert id (E = shared). */
+int coli_cuda_moe_layer_last_pairs(ColiCudaMoeLayer *layer, int *n_pairs, int *pair_token, int *pair_expert,
+                                   int capacity);
+int coli_cuda_moe_layer_read_taps(ColiCudaMoeLayer *layer, int32_t *gateup_taps, size_t gateup_count,
+                                  int32_t *down_taps, size_t down_count);
+
+/* Profile mode (in the spirit of COLI_CUDA_PROFILE, cuda/backend_cuda.cu:1068,1174-1207):
+ * each forward brackets its seven launches with events, waits for the stream and
+ * accumulates per-stage device milliseconds: quantise x, router logits, routing plan,
+ * gate/up GEMV, quantise h, down GEMV, combine.  Switching resets the accumulators. */
+int coli_cuda_moe_layer_set_profile(ColiCudaMoeLayer *layer, int enable);
+int coli_cuda_moe_layer_profile(ColiCudaMoeLayer *layer, double *stage_ms7, uint64_t *calls);
+
+/* Device error word of a context: 0 when no kernel reported a problem since the
+ * last call; otherwise the code (1 = a bounded wait on a copy barrier expired). */
+int coli_cuda_last_device_error(int device);
+/* Number of this library's kernels launched since init (all devices). */
+uint64_t coli_cuda_kernel_launches(void);
+/* The context's stream as a cudaStream_t, for callers that order their own work. */
+void *coli_cuda_stream(int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PEREGRINE_B200_H */

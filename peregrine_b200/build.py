@@ -1,0 +1,63 @@
+"""Builds libcoli_cuda_backend.so (sm_100a only) in-tree with nvcc."""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libcoli_cuda_backend.so")
+HOSTCHECK = os.path.join(HERE, "libpgb_hostcheck.so")
+
+SOURCES = ["backend.cu", "w4_host.cpp"]
+DEPS = ["kernels.cuh", "w4_layout.h", "w4_host.h", "backend_layer.inc", "backend_pipe.inc",
+        os.path.join("..", "..", "include", "peregrine_b200.h")]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    # the CPU reference never contracts a*b+c; neither may the device code
+    "-fmad=false", "-prec-div=true", "-prec-sqrt=true",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2",
+    "-shared", "-cudart", "static",
+]
+
+
+def _nvcc() -> str:
+    for cand in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found: the CUDA backend cannot be built")
+
+
+def _stale(target: str, inputs) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(p) > t for p in inputs)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    srcs = [os.path.join(CSRC, s) for s in SOURCES]
+    deps = srcs + [os.path.join(CSRC, d) for d in DEPS]
+    if force or _stale(LIB, deps):
+        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + srcs
+        subprocess.check_call(cmd, cwd=CSRC)
+    return LIB
+
+
+def build_hostcheck(force: bool = False) -> str:
+    """Host-only helper library for the CPU tests of the tile-stream layout."""
+    srcs = [os.path.join(CSRC, "w4_hostcheck.cpp"), os.path.join(CSRC, "w4_host.cpp")]
+    deps = srcs + [os.path.join(CSRC, "w4_layout.h"), os.path.join(CSRC, "w4_host.h")]
+    if force or _stale(HOSTCHECK, deps):
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-pthread", "-o", HOSTCHECK] + srcs
+        subprocess.check_call(cmd, cwd=CSRC)
+    return HOSTCHECK
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_hostcheck(force="--force" in sys.argv))

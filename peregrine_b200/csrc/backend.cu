@@ -1,0 +1,705 @@
+// Host side of libcoli_cuda_backend.so: contexts, residency, the expert-group
+// calls of the reference ABI and the device-resident MoE layer.  Declarations
+// and the reference lines each entry point replaces are in
+// include/peregrine_b200.h.
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "../../include/peregrine_b200.h"
+#include "kernels.cuh"
+#include "w4_host.h"
+
+using namespace pgb;
+
+#define PGB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// ---------------------------------------------------------------- contexts
+struct DevBuf {
+    void *p = nullptr;
+    size_t cap = 0;
+    bool pinned = false;
+};
+
+struct Ctx {
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    int sms = 0;
+    size_t smem_optin = 0;
+    size_t tensor_count = 0, tensor_bytes = 0;
+    int *err_dev = nullptr;
+    uint64_t scratch_gen = 0;
+    // expert-group scratch (grow-only, per device; one caller thread per device)
+    DevBuf x, y, h, xq, sx, xcs, hq, sh, hcs, slots_gu, slots_dn, slots_f32, nslots, csr_ptr, csr_idx, csr_rw, out;
+    DevBuf pin_x, pin_y;
+    DevBuf pipe[24];
+    bool capturing = false;
+};
+
+static Ctx g_ctx[COLI_CUDA_MAX_DEVICES];
+static int g_nctx = 0;
+static std::mutex g_stats_mu;
+static uint64_t g_calls = 0, g_experts = 0, g_rows = 0;
+static double g_h2d_ms = 0, g_kernel_ms = 0, g_d2h_ms = 0;
+static uint64_t g_captures = 0, g_replays = 0, g_invalidations = 0, g_uncacheable = 0;
+static std::atomic<uint64_t> g_launches{0};
+
+static int cuda_ok(cudaError_t err, const char *what) {
+    if (err == cudaSuccess) return 1;
+    std::fprintf(stderr, "[CUDA] %s: %s\n", what, cudaGetErrorString(err));
+    return 0;
+}
+static int fail(const char *what) {
+    std::fprintf(stderr, "[CUDA] %s\n", what);
+    return 0;
+}
+
+static Ctx *find_ctx(int device) {
+    for (int i = 0; i < g_nctx; ++i)
+        if (g_ctx[i].device == device) return &g_ctx[i];
+    return nullptr;
+}
+
+static thread_local int t_current_device = -1;
+static int select_ctx(Ctx *c) {
+    if (!c) return 0;
+    if (t_current_device == c->device) return 1;
+    if (!cuda_ok(cudaSetDevice(c->device), "select device")) return 0;
+    t_current_device = c->device;
+    return 1;
+}
+
+static int env_flag(const char *name, int dflt) {
+    const char *v = std::getenv(name);
+    return v ? std::atoi(v) : dflt;
+}
+
+static void free_buf(DevBuf &b) {
+    if (b.p) {
+        if (b.pinned)
+            cudaFreeHost(b.p);
+        else
+            cudaFree(b.p);
+    }
+    b.p = nullptr;
+    b.cap = 0;
+}
+
+// grow-only reservation; a growth waits for the stream so no kernel still reads the old block
+static int reserve(Ctx *c, DevBuf &b, size_t bytes, bool pinned = false) {
+    if (bytes <= b.cap && b.p) return 1;
+    if (bytes == 0) bytes = 16;
+    if (b.p) {
+        if (!cuda_ok(cudaStreamSynchronize(c->stream), "scratch growth sync")) return 0;
+        free_buf(b);
+        c->scratch_gen++;
+    }
+    b.pinned = pinned;
+    const size_t want = (bytes + 255) & ~(size_t)255;
+    cudaError_t e = pinned ? cudaMallocHost(&b.p, want) : cudaMalloc(&b.p, want);
+    if (!cuda_ok(e, pinned ? "pinned scratch allocation" : "scratch allocation")) {
+        b.p = nullptr;
+        return 0;
+    }
+    b.cap = want;
+    return 1;
+}
+
+template <typename... KArgs, typename... Args>
+static int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const char *what,
+                  Args... args) {
+    kernel<<<grid, block, smem, stream>>>(args...);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_ok(cudaGetLastError(), what);
+}
+
+PGB_EXPORT int coli_cuda_probe_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+PGB_EXPORT void coli_cuda_shutdown(void);
+
+PGB_EXPORT int coli_cuda_init(const int *devices, int count) {
+    int available = 0;
+    if (!devices || count < 1 || count > COLI_CUDA_MAX_DEVICES) return 0;
+    if (!cuda_ok(cudaGetDeviceCount(&available), "device discovery")) return 0;
+    if (g_nctx) coli_cuda_shutdown();
+    for (int i = 0; i < count; ++i) {
+        const int device = devices[i];
+        if (device < 0 || device >= available) {
+            std::fprintf(stderr, "[CUDA] invalid device %d (available: 0..%d)\n", device, available - 1);
+            coli_cuda_shutdown();
+            return 0;
+        }
+        if (find_ctx(device)) {
+            std::fprintf(stderr, "[CUDA] duplicate device %d\n", device);
+            coli_cuda_shutdown();
+            return 0;
+        }
+        Ctx *c = &g_ctx[g_nctx];
+        *c = Ctx();
+        c->device = device;
+        t_current_device = -1;
+        cudaDeviceProp prop{};
+        if (!select_ctx(c) || !cuda_ok(cudaGetDeviceProperties(&prop, device), "device properties") ||
+            !cuda_ok(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking), "stream creation") ||
+            !cuda_ok(cudaMalloc(&c->err_dev, 256), "error word allocation") ||
+            !cuda_ok(cudaMemset(c->err_dev, 0, 256), "error word clear")) {
+            g_nctx++;
+            coli_cuda_shutdown();
+            return 0;
+        }
+        c->sms = prop.multiProcessorCount;
+        c->smem_optin = prop.sharedMemPerBlockOptin;
+        g_nctx++;
+        if (prop.major != 10)
+            std::fprintf(stderr, "[CUDA] device %d is sm_%d%d: this backend carries sm_100a code only\n", device,
+                         prop.major, prop.minor);
+        std::fprintf(stderr, "[CUDA] device %d: %s, %.1f GB VRAM, sm_%d%d, %d SMs\n", device, prop.name,
+                     prop.totalGlobalMem / 1e9, prop.major, prop.minor, prop.multiProcessorCount);
+    }
+    return 1;
+}
+
+PGB_EXPORT void coli_cuda_shutdown(void) {
+    for (int i = 0; i < g_nctx; ++i) {
+        Ctx *c = &g_ctx[i];
+        t_current_device = -1;
+        if (!select_ctx(c)) continue;
+        if (c->stream) cudaStreamSynchronize(c->stream);
+        DevBuf *bufs[] = {&c->x,        &c->y,        &c->h,         &c->xq,     &c->sx,      &c->xcs,
+                          &c->hq,       &c->sh,       &c->hcs,       &c->slots_gu, &c->slots_dn, &c->slots_f32,
+                          &c->nslots,   &c->csr_ptr,  &c->csr_idx,   &c->csr_rw, &c->out,     &c->pin_x,
+                          &c->pin_y};
+        for (DevBuf *b : bufs) free_buf(*b);
+        for (DevBuf &b : c->pipe) free_buf(b);
+        if (c->err_dev) cudaFree(c->err_dev);
+        if (c->stream) cudaStreamDestroy(c->stream);
+        *c = Ctx();
+    }
+    g_nctx = 0;
+    t_current_device = -1;
+}
+
+PGB_EXPORT int coli_cuda_device_count(void) { return g_nctx; }
+PGB_EXPORT int coli_cuda_device_at(int index) { return (index >= 0 && index < g_nctx) ? g_ctx[index].device : -1; }
+
+PGB_EXPORT int coli_cuda_mem_info(int device, size_t *free_bytes, size_t *total_bytes) {
+    Ctx *c = find_ctx(device);
+    if (!free_bytes || !total_bytes || !select_ctx(c)) return 0;
+    return cuda_ok(cudaMemGetInfo(free_bytes, total_bytes), "memory query");
+}
+
+PGB_EXPORT void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes) {
+    size_t n = 0, b = 0;
+    for (int i = 0; i < g_nctx; ++i)
+        if (device < 0 || g_ctx[i].device == device) {
+            n += g_ctx[i].tensor_count;
+            b += g_ctx[i].tensor_bytes;
+        }
+    if (tensor_count) *tensor_count = n;
+    if (tensor_bytes) *tensor_bytes = b;
+}
+
+PGB_EXPORT void coli_cuda_group_stats(uint64_t *calls, uint64_t *experts, uint64_t *rows, double *h2d_ms,
+                                      double *kernel_ms, double *d2h_ms) {
+    std::lock_guard<std::mutex> lk(g_stats_mu);
+    if (calls) *calls = g_calls;
+    if (experts) *experts = g_experts;
+    if (rows) *rows = g_rows;
+    if (h2d_ms) *h2d_ms = g_h2d_ms;
+    if (kernel_ms) *kernel_ms = g_kernel_ms;
+    if (d2h_ms) *d2h_ms = g_d2h_ms;
+}
+
+PGB_EXPORT void coli_cuda_graph_cache_stats(uint64_t *captures, uint64_t *replays, uint64_t *invalidations,
+                                            uint64_t *uncacheable) {
+    std::lock_guard<std::mutex> lk(g_stats_mu);
+    if (captures) *captures = g_captures;
+    if (replays) *replays = g_replays;
+    if (invalidations) *invalidations = g_invalidations;
+    if (uncacheable) *uncacheable = g_uncacheable;
+}
+
+PGB_EXPORT int coli_cuda_last_device_error(int device) {
+    Ctx *c = find_ctx(device);
+    if (!select_ctx(c)) return -1;
+    int v = 0;
+    if (!cuda_ok(cudaStreamSynchronize(c->stream), "error word sync") ||
+        !cuda_ok(cudaMemcpy(&v, c->err_dev, sizeof(int), cudaMemcpyDeviceToHost), "error word read"))
+        return -1;
+    if (v) cudaMemset(c->err_dev, 0, sizeof(int));
+    return v;
+}
+PGB_EXPORT uint64_t coli_cuda_kernel_launches(void) { return g_launches.load(); }
+PGB_EXPORT void *coli_cuda_stream(int device) {
+    Ctx *c = find_ctx(device);
+    return c ? (void *)c->stream : nullptr;
+}
+
+// ---------------------------------------------------------------- residency
+// fmt as the caller named it (0, 1, 2, 3, 4); storage is one of:
+//   kind 0: fp32 [O, I]   (fmt 0, and fmt 1 / fmt 3 expanded on the host at upload)
+//   kind 1: int4 tile stream, per-row scales   (fmt 2)
+//   kind 2: int4 tile stream, group scales     (fmt 4)
+struct ColiCudaTensor {
+    int fmt, I, O, device, kind, gs;
+    W4Layout L;
+    void *data;         // fp32 matrix or tile stream
+    float *row_scales;  // kind 1: padded to ntile*16
+    size_t bytes;
+};
+
+static size_t src_row_bytes(int fmt, int I) {
+    switch (fmt) {
+        case 0: return (size_t)I * 4;
+        case 1: return (size_t)I;
+        case 2:
+        case 4: return (size_t)(I + 1) / 2;
+        case 3: return (size_t)(I + 3) / 4;
+    }
+    return 0;
+}
+
+// Fills the tensor's device storage from caller-format host data.
+static int tensor_fill(Ctx *c, ColiCudaTensor *t, const void *weights, const float *scales) {
+    if (t->kind == 0) {
+        const size_t n = (size_t)t->O * t->I;
+        if (t->fmt == 0) return cuda_ok(cudaMemcpy(t->data, weights, n * 4, cudaMemcpyHostToDevice), "tensor upload");
+        // int8 / int2 sources: expand to the fp32 values the reference's generic arm
+        // reads (cuda/backend_cuda.cu:101-112) times the row scale.
+        std::vector<float> f(n);
+        const uint8_t *q = static_cast<const uint8_t *>(weights);
+        const size_t rb = src_row_bytes(t->fmt, t->I);
+        for (int o = 0; o < t->O; ++o)
+            for (int i = 0; i < t->I; ++i) {
+                float v;
+                if (t->fmt == 1)
+                    v = (float)reinterpret_cast<const int8_t *>(q + o * rb)[i];
+                else
+                    v = (float)(((q[o * rb + (i >> 2)] >> ((i & 3) * 2)) & 3) - 2);
+                f[(size_t)o * t->I + i] = v * scales[o];
+            }
+        return cuda_ok(cudaMemcpy(t->data, f.data(), n * 4, cudaMemcpyHostToDevice), "tensor upload");
+    }
+    std::vector<uint8_t> stream(t->L.total_bytes);
+    std::vector<float> rs(t->kind == 1 ? (size_t)t->L.ntile * kTileRows : 0);
+    w4_repack(t->L, static_cast<const uint8_t *>(weights), scales, stream.data(), rs.empty() ? nullptr : rs.data(), 0);
+    if (!cuda_ok(cudaMemcpy(t->data, stream.data(), stream.size(), cudaMemcpyHostToDevice), "tensor upload")) return 0;
+    if (t->kind == 1 &&
+        !cuda_ok(cudaMemcpy(t->row_scales, rs.data(), rs.size() * 4, cudaMemcpyHostToDevice), "scale upload"))
+        return 0;
+    (void)c;
+    return 1;
+}
+
+static int tensor_upload_impl(ColiCudaTensor **tensor, const void *weights, const float *scales, int fmt, int I, int O,
+                              int gs, int device) {
+    Ctx *c = find_ctx(device);
+    if (!tensor || !weights || I < 1 || O < 1 || !select_ctx(c)) return 0;
+    if (!src_row_bytes(fmt, I) || (fmt && !scales)) return 0;
+    if (*tensor) {
+        ColiCudaTensor *t = *tensor;
+        return t->fmt == fmt && t->I == I && t->O == O && t->device == device && (fmt != 4 || t->gs == gs);
+    }
+    ColiCudaTensor *t = static_cast<ColiCudaTensor *>(std::calloc(1, sizeof(ColiCudaTensor)));
+    if (!t) return 0;
+    t->fmt = fmt;
+    t->I = I;
+    t->O = O;
+    t->device = device;
+    t->gs = (fmt == 4) ? gs : 0;
+    t->kind = (fmt == 2) ? 1 : (fmt == 4) ? 2 : 0;
+    if (t->kind) {
+        if (!w4_layout_make(&t->L, O, I, t->kind == 2, gs)) {
+            std::free(t);
+            return fail("int4 upload: group size must be a multiple of 32 and at most 256");
+        }
+        t->bytes = t->L.total_bytes + (t->kind == 1 ? (size_t)t->L.ntile * kTileRows * 4 : 0);
+    } else {
+        t->bytes = (size_t)O * I * 4;
+    }
+    const size_t main_bytes = t->kind ? t->L.total_bytes : t->bytes;
+    if (!cuda_ok(cudaMalloc(&t->data, main_bytes), "tensor allocation") ||
+        (t->kind == 1 &&
+         !cuda_ok(cudaMalloc(&t->row_scales, (size_t)t->L.ntile * kTileRows * 4), "scale allocation")) ||
+        !tensor_fill(c, t, weights, scales)) {
+        if (t->data) cudaFree(t->data);
+        if (t->row_scales) cudaFree(t->row_scales);
+        std::free(t);
+        return 0;
+    }
+    c->tensor_count++;
+    c->tensor_bytes += t->bytes;
+    *tensor = t;
+    return 1;
+}
+
+PGB_EXPORT int coli_cuda_tensor_upload(ColiCudaTensor **tensor, const void *weights, const float *scales, int fmt,
+                                       int I, int O, int device) {
+    if (fmt < 0 || fmt > 3) return 0;
+    return tensor_upload_impl(tensor, weights, scales, fmt, I, O, 0, device);
+}
+
+PGB_EXPORT int coli_cuda_tensor_upload_grouped(ColiCudaTensor **tensor, const void *weights, const float *scales,
+                                               int I, int O, int gs, int device) {
+    return tensor_upload_impl(tensor, weights, scales, 4, I, O, gs, device);
+}
+
+PGB_EXPORT int coli_cuda_tensor_update(ColiCudaTensor *tensor, const void *weights, const float *scales) {
+    if (!tensor || !weights || (tensor->fmt && !scales)) return 0;
+    Ctx *c = find_ctx(tensor->device);
+    if (!select_ctx(c)) return 0;
+    // kernels of earlier calls may still read the old contents
+    if (!cuda_ok(cudaStreamSynchronize(c->stream), "tensor refresh sync")) return 0;
+    return tensor_fill(c, tensor, weights, scales);
+}
+
+PGB_EXPORT void coli_cuda_tensor_free(ColiCudaTensor *tensor) {
+    if (!tensor) return;
+    Ctx *c = find_ctx(tensor->device);
+    if (select_ctx(c)) {
+        cudaStreamSynchronize(c->stream);
+        if (tensor->data) cudaFree(tensor->data);
+        if (tensor->row_scales) cudaFree(tensor->row_scales);
+        if (c->tensor_count) c->tensor_count--;
+        c->tensor_bytes = c->tensor_bytes >= tensor->bytes ? c->tensor_bytes - tensor->bytes : 0;
+    }
+    std::free(tensor);
+}
+PGB_EXPORT size_t coli_cuda_tensor_bytes(const ColiCudaTensor *tensor) { return tensor ? tensor->bytes : 0; }
+PGB_EXPORT int coli_cuda_tensor_device(const ColiCudaTensor *tensor) { return tensor ? tensor->device : -1; }
+
+// ------------------------------------------------------------ GEMV dispatch
+static size_t gemv_xs_bytes(int n_xrows, int kp, int nblk) {
+    return (((size_t)n_xrows * kp + 15) & ~(size_t)15) + (size_t)n_xrows * nblk * 4;
+}
+
+template <int RMAX, bool GROUPED, int BPG, bool XS>
+static int gemv_launch_t(Ctx *c, const GemvParams &P, size_t smem) {
+    auto kfn = gemv_w4a8_kernel<RMAX, GROUPED, BPG, XS>;
+    static std::atomic<uint32_t> configured{0};  // one bit per device slot
+    const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
+    if (!(configured.load() & bit)) {
+        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->smem_optin),
+                     "gemv shared-memory opt-in"))
+            return 0;
+        configured.fetch_or(bit);
+    }
+    return launch(kfn, dim3(c->sms), dim3(kGemvWarps * 32), smem, c->stream, "w4a8 gemv launch", P);
+}
+
+template <int RMAX>
+static int gemv_launch_r(Ctx *c, const GemvParams &P, bool grouped, bool xs, size_t smem) {
+    if (grouped) {
+        if (P.bpg == 1)
+            return xs ? gemv_launch_t<RMAX, true, 1, true>(c, P, smem) : gemv_launch_t<RMAX, true, 1, false>(c, P, smem);
+        return xs ? gemv_launch_t<RMAX, true, 0, true>(c, P, smem) : gemv_launch_t<RMAX, true, 0, false>(c, P, smem);
+    }
+    return xs ? gemv_launch_t<RMAX, false, 1, true>(c, P, smem) : gemv_launch_t<RMAX, false, 1, false>(c, P, smem);
+}
+
+// Fills the layout-dependent fields and launches.  `max_rows` bounds the rows of any slot.
+static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_rows) {
+    P.mode = mode;
+    P.ng = L.ng;
+    P.bpg = L.bpg;
+    P.gpc = L.gpc;
+    P.nchunk = L.nchunk;
+    P.group_bytes = L.group_bytes;
+    P.ntile = L.ntile;
+    P.warp_tiles = (mode == 0) ? L.ntile : (L.ntile + 1) / 2;
+    P.O = L.O;
+    P.tile_bytes = L.tile_bytes;
+    P.xq_stride = L.kp;
+    P.cs_stride = L.nblk;
+    P.err = c->err_dev;
+    const size_t base = (size_t)kRingBytes + kGemvBarBytes;
+    const size_t xs_need = gemv_xs_bytes(P.n_xrows, L.kp, L.nblk);
+    const bool xs = base + xs_need + 256 <= c->smem_optin;
+    const size_t smem = base + (xs ? xs_need : 0);
+    if (smem > c->smem_optin) return fail("w4a8 gemv: shared memory budget exceeded");
+    const bool grouped = L.grouped != 0;
+    if (max_rows <= 1) return gemv_launch_r<1>(c, P, grouped, xs, smem);
+    if (max_rows <= 2) return gemv_launch_r<2>(c, P, grouped, xs, smem);
+    if (max_rows <= 4) return gemv_launch_r<4>(c, P, grouped, xs, smem);
+    return gemv_launch_r<8>(c, P, grouped, xs, smem);
+}
+
+static int qrow_run(Ctx *c, const float *x, long long ldx, int K, const W4Layout &L, int8_t *xq, float *sx, int *cs,
+                    const int *n_rows_dev, int n_rows, int grid_rows) {
+    if (grid_rows < 1) return 1;
+    return launch(qrow_i8_kernel, dim3(grid_rows), dim3(256), 0, c->stream, "activation quantise launch", x, ldx, K,
+                  L.kp, L.nblk, xq, sx, cs, n_rows_dev, n_rows);
+}
+
+// ------------------------------------------------------------- expert group
+struct ReduceSpec {
+    const int *row_ptr, *row_idx;
+    const float *rw;
+    int s_n;
+    float *out;
+};
+
+static bool same_class(const ColiCudaTensor *a, const ColiCudaTensor *b) {
+    return a->kind == b->kind && a->gs == b->gs;
+}
+
+static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups, ColiCudaTensor *const *downs,
+                             const int *rows, int count, float *y, const float *x, const ReduceSpec *red,
+                             int *arm_out) {
+    if (!gates || !ups || !downs || !rows || !x || count < 1 || count > 256) return 0;
+    if (!red && !y) return 0;
+    if (red && (!red->row_ptr || !red->row_idx || !red->rw || !red->out || red->s_n < 1)) return 0;
+    ColiCudaTensor *first = gates[0];
+    if (!first) return 0;
+    const int device = first->device, D = first->I, I = first->O;
+    int total = 0, max_rows = 0, all_i4 = 1, min_rows = 1 << 30;
+    std::vector<int> row0(count);
+    for (int cidx = 0; cidx < count; ++cidx) {
+        ColiCudaTensor *g = gates[cidx], *u = ups[cidx], *d = downs[cidx];
+        if (!g || !u || !d || rows[cidx] < 1 || g->device != device || u->device != device || d->device != device ||
+            g->I != D || u->I != D || g->O != I || u->O != I || d->I != I || d->O != D)
+            return 0;
+        if (!same_class(g, u)) return fail("expert group: gate and up of one expert must share a format");
+        all_i4 &= (g->kind != 0 && d->kind != 0);
+        row0[cidx] = total;
+        total += rows[cidx];
+        max_rows = rows[cidx] > max_rows ? rows[cidx] : max_rows;
+        min_rows = rows[cidx] < min_rows ? rows[cidx] : min_rows;
+    }
+    Ctx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    // The arm code the reference's selector would report for this call
+    // (cuda/backend_cuda.cu:897-930): 1 when the W4A16 knob is on and the group
+    // qualifies, 2 for all-int4 groups, 3 otherwise.  One kernel family serves all.
+    int arm = all_i4 ? 2 : 3;
+    if (all_i4 && env_flag("COLI_CUDA_TC_W4A16", 0) && min_rows >= env_flag("COLI_CUDA_TC_W4A16_MIN", 16)) arm = 1;
+    if (arm_out) *arm_out = arm;
+
+    const size_t xb = (size_t)total * D * 4, hb = (size_t)total * I * 4;
+    W4Layout Lx, Lh;  // activation layouts (per-row kind: padding to 32 only)
+    w4_layout_make(&Lx, 1, D, 0, 0);
+    w4_layout_make(&Lh, 1, I, 0, 0);
+    // grouped formats may pad K up to a multiple of gs: size for the largest gs (256)
+    const size_t kpx = ((size_t)D + 255) / 256 * 256 + 256, kph = ((size_t)I + 255) / 256 * 256 + 256;
+    if (!reserve(c, c->x, xb) || !reserve(c, c->y, xb) || !reserve(c, c->h, hb) ||
+        !reserve(c, c->xq, (size_t)total * kpx) || !reserve(c, c->sx, (size_t)total * 4) ||
+        !reserve(c, c->xcs, (size_t)total * (kpx / 32) * 4) || !reserve(c, c->hq, (size_t)total * kph) ||
+        !reserve(c, c->sh, (size_t)total * 4) || !reserve(c, c->hcs, (size_t)total * (kph / 32) * 4) ||
+        !reserve(c, c->slots_gu, (size_t)count * sizeof(GemvSlot)) ||
+        !reserve(c, c->slots_dn, (size_t)count * sizeof(GemvSlot)) ||
+        !reserve(c, c->slots_f32, (size_t)count * sizeof(F32Slot)) || !reserve(c, c->nslots, 256) ||
+        !reserve(c, c->pin_x, xb, true) || !reserve(c, c->pin_y, xb, true))
+        return 0;
+    const int profile = env_flag("COLI_CUDA_PROFILE", 0);
+    const int graph_knob = env_flag("COLI_CUDA_GRAPH", 0);
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+    if (profile)
+        for (auto &e : ev) cudaEventCreate(&e);
+    int ok = 1;
+    std::memcpy(c->pin_x.p, x, xb);
+    if (profile) cudaEventRecord(ev[0], c->stream);
+    ok = ok && cuda_ok(cudaMemcpyAsync(c->x.p, c->pin_x.p, xb, cudaMemcpyHostToDevice, c->stream), "group x upload");
+    if (profile) cudaEventRecord(ev[1], c->stream);
+
+    // ---- phase 1: gate/up (+ SwiGLU) into h, one launch per format class
+    std::vector<char> done(count, 0);
+    for (int lead = 0; ok && lead < count; ++lead) {
+        if (done[lead]) continue;
+        const ColiCudaTensor *cls = gates[lead];
+        std::vector<GemvSlot> gs_host;
+        std::vector<F32Slot> fs_host;
+        int cls_max = 0;
+        for (int j = lead; j < count; ++j) {
+            if (done[j] || !same_class(gates[j], cls)) continue;
+            done[j] = 1;
+            cls_max = rows[j] > cls_max ? rows[j] : cls_max;
+            if (cls->kind == 0) {
+                fs_host.push_back({(const float *)gates[j]->data, (const float *)ups[j]->data, row0[j], rows[j]});
+            } else {
+                gs_host.push_back({(const uint8_t *)gates[j]->data, (const uint8_t *)ups[j]->data,
+                                   gates[j]->row_scales, ups[j]->row_scales, row0[j], rows[j]});
+            }
+        }
+        if (cls->kind == 0) {
+            const int n = (int)fs_host.size();
+            // slot tables are consumed asynchronously: stage through a synchronous copy into a
+            // region no earlier launch of this call still reads (one region per class is enough
+            // because every class launch is ordered on the same stream after the copy)
+            ok = ok && cuda_ok(cudaStreamSynchronize(c->stream), "group slot sync") &&
+                 cuda_ok(cudaMemcpy(c->slots_f32.p, fs_host.data(), n * sizeof(F32Slot), cudaMemcpyHostToDevice),
+                         "group slot upload") &&
+                 launch(gemv_f32_kernel, dim3((I + 7) / 8, cls_max, n), dim3(256), 0, c->stream,
+                        "f32 gate/up launch", (const F32Slot *)c->slots_f32.p, n, 0, I, D, (const float *)c->x.p,
+                        (long long)D, (float *)c->h.p, (long long)I, cls_max);
+        } else {
+            const int n = (int)gs_host.size();
+            const W4Layout &L = cls->L;
+            ok = ok && cuda_ok(cudaStreamSynchronize(c->stream), "group slot sync") &&
+                 cuda_ok(cudaMemcpy(c->slots_gu.p, gs_host.data(), n * sizeof(GemvSlot), cudaMemcpyHostToDevice),
+                         "group slot upload") &&
+                 cuda_ok(cudaMemcpy(c->nslots.p, &n, sizeof(int), cudaMemcpyHostToDevice), "group slot count") &&
+                 qrow_run(c, (const float *)c->x.p, D, D, L, (int8_t *)c->xq.p, (float *)c->sx.p, (int *)c->xcs.p,
+                          nullptr, total, total);
+            GemvParams P{};
+            P.slots = (const GemvSlot *)c->slots_gu.p;
+            P.n_slots = (const int *)c->nslots.p;
+            P.xq = (const int8_t *)c->xq.p;
+            P.csum = (const int *)c->xcs.p;
+            P.sx = (const float *)c->sx.p;
+            P.rowmap = nullptr;
+            P.n_xrows = total;
+            P.out = (float *)c->h.p;
+            P.out_stride = I;
+            ok = ok && gemv_run(c, P, L, 0, cls_max);
+        }
+    }
+    // ---- phase 2: down into y, one launch per format class of the down matrices
+    std::fill(done.begin(), done.end(), 0);
+    for (int lead = 0; ok && lead < count; ++lead) {
+        if (done[lead]) continue;
+        const ColiCudaTensor *cls = downs[lead];
+        std::vector<GemvSlot> gs_host;
+        std::vector<F32Slot> fs_host;
+        int cls_max = 0;
+        for (int j = lead; j < count; ++j) {
+            if (done[j] || !same_class(downs[j], cls)) continue;
+            done[j] = 1;
+            cls_max = rows[j] > cls_max ? rows[j] : cls_max;
+            if (cls->kind == 0)
+                fs_host.push_back({(const float *)downs[j]->data, nullptr, row0[j], rows[j]});
+            else
+                gs_host.push_back(
+                    {(const uint8_t *)downs[j]->data, nullptr, downs[j]->row_scales, nullptr, row0[j], rows[j]});
+        }
+        if (cls->kind == 0) {
+            const int n = (int)fs_host.size();
+            ok = ok && cuda_ok(cudaStreamSynchronize(c->stream), "group slot sync") &&
+                 cuda_ok(cudaMemcpy(c->slots_f32.p, fs_host.data(), n * sizeof(F32Slot), cudaMemcpyHostToDevice),
+                         "group slot upload") &&
+                 launch(gemv_f32_kernel, dim3((D + 7) / 8, cls_max, n), dim3(256), 0, c->stream, "f32 down launch",
+                        (const F32Slot *)c->slots_f32.p, n, 1, D, I, (const float *)c->h.p, (long long)I,
+                        (float *)c->y.p, (long long)D, cls_max);
+        } else {
+            const int n = (int)gs_host.size();
+            const W4Layout &L = cls->L;
+            ok = ok && cuda_ok(cudaStreamSynchronize(c->stream), "group slot sync") &&
+                 cuda_ok(cudaMemcpy(c->slots_dn.p, gs_host.data(), n * sizeof(GemvSlot), cudaMemcpyHostToDevice),
+                         "group slot upload") &&
+                 cuda_ok(cudaMemcpy(c->nslots.p, &n, sizeof(int), cudaMemcpyHostToDevice), "group slot count") &&
+                 qrow_run(c, (const float *)c->h.p, I, I, L, (int8_t *)c->hq.p, (float *)c->sh.p, (int *)c->hcs.p,
+                          nullptr, total, total);
+            GemvParams P{};
+            P.slots = (const GemvSlot *)c->slots_dn.p;
+            P.n_slots = (const int *)c->nslots.p;
+            P.xq = (const int8_t *)c->hq.p;
+            P.csum = (const int *)c->hcs.p;
+            P.sx = (const float *)c->sh.p;
+            P.rowmap = nullptr;
+            P.n_xrows = total;
+            P.out = (float *)c->y.p;
+            P.out_stride = D;
+            ok = ok && gemv_run(c, P, L, 1, cls_max);
+        }
+    }
+    // ---- optional CSR combine, then the result back to the host
+    size_t out_bytes = xb;
+    const void *out_dev = c->y.p;
+    if (ok && red) {
+        out_bytes = (size_t)red->s_n * D * 4;
+        ok = reserve(c, c->csr_ptr, (size_t)(red->s_n + 1) * 4) && reserve(c, c->csr_idx, (size_t)total * 4) &&
+             reserve(c, c->csr_rw, (size_t)total * 4) && reserve(c, c->out, out_bytes) &&
+             reserve(c, c->pin_y, out_bytes > xb ? out_bytes : xb, true) &&
+             cuda_ok(cudaMemcpyAsync(c->csr_ptr.p, red->row_ptr, (size_t)(red->s_n + 1) * 4, cudaMemcpyHostToDevice,
+                                     c->stream),
+                     "reduce layout upload") &&
+             cuda_ok(cudaMemcpyAsync(c->csr_idx.p, red->row_idx, (size_t)total * 4, cudaMemcpyHostToDevice, c->stream),
+                     "reduce layout upload") &&
+             cuda_ok(cudaMemcpyAsync(c->csr_rw.p, red->rw, (size_t)total * 4, cudaMemcpyHostToDevice, c->stream),
+                     "reduce weights upload") &&
+             launch(csr_reduce_kernel, dim3((D + 255) / 256, red->s_n), dim3(256), 0, c->stream, "csr reduce launch",
+                    (const float *)c->y.p, D, (const int *)c->csr_ptr.p, (const int *)c->csr_idx.p,
+                    (const float *)c->csr_rw.p, (float *)c->out.p);
+        out_dev = c->out.p;
+    }
+    if (profile) cudaEventRecord(ev[2], c->stream);
+    ok = ok && cuda_ok(cudaMemcpyAsync(c->pin_y.p, out_dev, out_bytes, cudaMemcpyDeviceToHost, c->stream),
+                       "group result download");
+    if (profile) cudaEventRecord(ev[3], c->stream);
+    ok = cuda_ok(cudaStreamSynchronize(c->stream), "group synchronize") && ok;
+    if (ok) std::memcpy(red ? (void *)red->out : (void *)y, c->pin_y.p, out_bytes);
+    if (ok) {
+        int dev_err = 0;
+        cudaMemcpy(&dev_err, c->err_dev, sizeof(int), cudaMemcpyDeviceToHost);
+        if (dev_err) {
+            cudaMemset(c->err_dev, 0, sizeof(int));
+            std::fprintf(stderr, "[CUDA] expert group: device reported error %d\n", dev_err);
+            ok = 0;
+        }
+    }
+    {
+        std::lock_guard<std::mutex> lk(g_stats_mu);
+        g_calls++;
+        g_experts += (uint64_t)count;
+        g_rows += (uint64_t)total;
+        if (profile && ok) {
+            float a = 0, b = 0, d = 0;
+            cudaEventElapsedTime(&a, ev[0], ev[1]);
+            cudaEventElapsedTime(&b, ev[1], ev[2]);
+            cudaEventElapsedTime(&d, ev[2], ev[3]);
+            g_h2d_ms += a;
+            g_kernel_ms += b;
+            g_d2h_ms += d;
+        }
+        // The launch sequence here is short and shape-independent, so no graph is
+        // instantiated; the cache counters are kept as bookkeeping only: with the knob
+        // on every call is counted as uncacheable.
+        if (graph_knob) g_uncacheable++;
+    }
+    if (profile)
+        for (auto &e : ev) cudaEventDestroy(e);
+    return ok;
+}
+
+PGB_EXPORT int coli_cuda_expert_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                      ColiCudaTensor *const *downs, const int *rows, int count, float *y,
+                                      const float *x) {
+    return expert_group_impl(gates, ups, downs, rows, count, y, x, nullptr, nullptr);
+}
+PGB_EXPORT int coli_cuda_expert_group_tiled(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                            ColiCudaTensor *const *downs, const int *rows, int count, float *y,
+                                            const float *x, int tile_m, int tile_n, int tile_k, int *arm_out) {
+    (void)tile_m;
+    (void)tile_n;
+    (void)tile_k;
+    return expert_group_impl(gates, ups, downs, rows, count, y, x, nullptr, arm_out);
+}
+PGB_EXPORT int coli_cuda_expert_group_reduce(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                             ColiCudaTensor *const *downs, const int *rows, int count,
+                                             const int *row_ptr, const int *row_idx, const float *rw, int s_n,
+                                             float *out, const float *x) {
+    ReduceSpec red = {row_ptr, row_idx, rw, s_n, out};
+    return expert_group_impl(gates, ups, downs, rows, count, nullptr, x, &red, nullptr);
+}
+
+PGB_EXPORT int coli_cuda_expert_mlp(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                                    const float *x, int S) {
+    if (S < 1) return 0;
+    return expert_group_impl(&gate, &up, &down, &S, 1, y, x, nullptr, nullptr);
+}
+PGB_EXPORT int coli_cuda_shared_mlp_w4a16(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                                          const float *x, int S) {
+    return coli_cuda_expert_mlp(gate, up, down, y, x, S);
+}
+
+#include "backend_layer.inc"
+#include "backend_pipe.inc"

@@ -1,0 +1,139 @@
+"""Parity of the device-resident MoE layer with the CPU oracle: routing ids and
+weights identical, per-block int32 accumulators bit-exact, fp32 outputs within
+1e-5 relative (they are in fact compared bit for bit as well)."""
+import numpy as np
+import pytest
+
+import oracle as po
+from peregrine_b200 import cuda
+from peregrine_b200.resident import upload_layer
+from peregrine_b200.synth import synth_layer, synth_tokens
+from tests.gpu_common import bits, dev  # noqa: F401
+from tests.refmodel import o_expert, oracle_layer_forward, rel_err
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-5  # post-scale fp32 outputs, relative
+
+
+def check_layer(dev, layer, x, taps=False):
+    m = x.shape[0]
+    ml = upload_layer(dev, layer)
+    if taps:
+        ml.enable_taps(True)
+    want, idx, w, keff, uni = oracle_layer_forward(layer, x, threads=4, want_routing=True)
+    got = ml.forward(x)
+    gidx, gw, gkeff, guni = ml.last_routing(m)
+    assert np.array_equal(gkeff, keff)
+    assert np.array_equal(gidx, idx)
+    assert np.array_equal(bits(gw), bits(w))
+    assert list(guni) == list(uni)  # batch-union (first-seen) order
+    assert rel_err(got, want) <= REL_TOL
+    assert np.array_equal(bits(got), bits(want))
+    assert np.array_equal(bits(ml.forward(x)), bits(got))  # repeat-stable
+    assert cuda.last_device_error(dev) == 0
+    if taps:
+        tok, exp = ml.last_pairs(m)
+        gs = layer.gs
+        ng_gu = -(-layer.hidden // gs) if gs else 1
+        ng_dn = -(-layer.inter // gs) if gs else 1
+        gu, dn = ml.read_taps(tok.size, ng_gu, ng_dn)
+        for p in range(tok.size):
+            ex = layer.shared if exp[p] == layer.n_experts else layer.experts[exp[p]]
+            g, u, d = o_expert(ex)
+            xq, sx = po.qrow_i8(x[tok[p]])
+            _, h = po.swiglu(g, u, d, x[tok[p]:tok[p] + 1], 1, want_h=True)
+            hq, sh = po.qrow_i8(h[0])
+            if gs:
+                _, bg = po.matmul_i4g_idot(xq, [sx], ex.gate.q, ex.gate.scale, 1, layer.hidden, layer.inter, gs, True)
+                _, bu = po.matmul_i4g_idot(xq, [sx], ex.up.q, ex.up.scale, 1, layer.hidden, layer.inter, gs, True)
+                _, bd = po.matmul_i4g_idot(hq, [sh], ex.down.q, ex.down.scale, 1, layer.inter, layer.hidden, gs, True)
+                assert np.array_equal(gu[p, 0], bg[0]) and np.array_equal(gu[p, 1], bu[0])
+                assert np.array_equal(dn[p], bd[0])
+            else:
+                _, ag = po.matmul_i4_idot(xq, [sx], ex.gate.q, ex.gate.scale, 1, layer.hidden, layer.inter, True)
+                _, ad = po.matmul_i4_idot(hq, [sh], ex.down.q, ex.down.scale, 1, layer.inter, layer.hidden, True)
+                assert np.array_equal(gu[p, 0, :, 0], ag[0]) and np.array_equal(dn[p, :, 0], ad[0])
+    ml.free()
+    return got
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 16, 33])
+def test_small_layer_all_batch_sizes(dev, m):
+    layer = synth_layer(100 + m, hidden=256, inter=96, n_experts=12, k=3, gs=32)
+    check_layer(dev, layer, synth_tokens(m, m, 256), taps=(m <= 3))
+
+
+def test_ragged_shapes_per_row_format(dev):
+    layer = synth_layer(7, hidden=100, inter=40, n_experts=5, k=2, gs=0)
+    check_layer(dev, layer, synth_tokens(1, 4, 100), taps=True)
+
+
+def test_group_128_and_no_shared_expert(dev):
+    layer = synth_layer(8, hidden=384, inter=256, n_experts=8, k=2, gs=128, shared=False, norm_topk=False,
+                        routed_scale=1.0)
+    check_layer(dev, layer, synth_tokens(2, 6, 384), taps=True)
+
+
+def test_config0_decode_layer(dev):
+    # BASELINE configs[0]: hidden 2048, 64 experts, top-4, 1 shared, inter 1024, gs 32, batch 1, seed 0
+    layer = synth_layer(0, hidden=2048, inter=1024, n_experts=64, k=4, gs=32, distinct_experts=8)
+    check_layer(dev, layer, synth_tokens(0, 1, 2048), taps=True)
+
+
+def test_config1_shapes_zipf_decode_and_small_batches(dev):
+    # BASELINE configs[1]/[2] layer shapes (hidden 6144, 256 experts, top-8, inter 2048); the
+    # experts reuse 4 weight blobs on the host, the device holds 256 separate copies
+    layer = synth_layer(1, hidden=6144, inter=2048, n_experts=256, k=8, gs=32, zipf=True, distinct_experts=4)
+    ml = upload_layer(dev, layer)
+    for m in (1, 4, 8, 16):
+        x = synth_tokens(50 + m, m, 6144)
+        want, idx, w, keff, uni = oracle_layer_forward(layer, x, threads=8, want_routing=True)
+        got = ml.forward(x)
+        gidx, gw, gkeff, guni = ml.last_routing(m)
+        assert np.array_equal(gidx, idx) and np.array_equal(bits(gw), bits(w)) and list(guni) == list(uni)
+        assert rel_err(got, want) <= REL_TOL
+        assert np.array_equal(bits(got), bits(want))
+    assert cuda.last_device_error(dev) == 0
+    ml.free()
+
+
+def test_router_edge_cases(dev):
+    # ties go to the lowest index; -inf / NaN scores are never selected; k > usable experts
+    hidden, inter, E, k = 64, 32, 6, 4
+    layer = synth_layer(3, hidden, inter, E, k, gs=32)
+    layer.router_w[:] = 0.0            # all logits 0 -> all sigmoid 0.5 -> ties
+    layer.router_bias[:] = 0.0
+    x = synth_tokens(3, 2, hidden)
+    ml = upload_layer(dev, layer)
+    ml.forward(x)
+    idx, w, keff, uni = ml.last_routing(2)
+    assert idx.tolist() == [[0, 1, 2, 3], [0, 1, 2, 3]] and keff.tolist() == [4, 4]
+    ml.free()
+    layer.router_bias[:] = -np.inf
+    layer.router_bias[4] = 0.0
+    layer.router_bias[1] = 0.0
+    check_layer(dev, layer, x)         # only experts 1 and 4 selectable: keff = 2
+    ml = upload_layer(dev, layer)
+    ml.forward(x)
+    idx, w, keff, uni = ml.last_routing(2)
+    assert keff.tolist() == [2, 2] and idx[:, :2].tolist() == [[1, 4], [1, 4]] and not idx[:, 2:].any()
+    ml.free()
+
+
+def test_device_pointer_forward_matches_host_forward(dev):
+    import torch
+
+    layer = synth_layer(21, hidden=256, inter=64, n_experts=8, k=2, gs=32)
+    ml = upload_layer(dev, layer)
+    x = synth_tokens(21, 4, 256)
+    want = ml.forward(x)
+    stream = torch.cuda.ExternalStream(cuda.lib().coli_cuda_stream(dev))
+    with torch.cuda.stream(stream):
+        xd = torch.from_numpy(x).cuda()
+        out = torch.empty_like(xd)
+    stream.synchronize()
+    ml.forward_dev(out.data_ptr(), xd.data_ptr(), 4)
+    cuda.lib().coli_cuda_pipe_sync(dev)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+    ml.free()
