@@ -346,11 +346,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="tokens per step (decode batch)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--experts", type=int, default=CFG["n_experts"],
+                    help="routed experts resident (smaller values are for profiler captures only)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     args.warmup = max(args.warmup, 3)
+    CFG["n_experts"] = args.experts
     if args.impl == "reference":
         run_reference(args, rank, world)
     else:
