@@ -28,3 +28,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def dev():
+    """One backend context on device 0 for the whole GPU test session."""
+    from peregrine_b200 import cuda
+
+    n = cuda.init([0])
+    if n < 1:
+        pytest.fail("a CUDA device is visible to torch but the backend could not initialise it")
+    yield 0
+    cuda.shutdown()

@@ -11,7 +11,7 @@ import oracle as po
 from peregrine_b200 import cuda
 from peregrine_b200.resident import upload_expert
 from peregrine_b200.synth import synth_expert
-from tests.gpu_common import bits, dev  # noqa: F401
+from tests.gpu_common import bits
 from tests.refmodel import o_expert
 
 pytestmark = pytest.mark.gpu

@@ -8,7 +8,7 @@ import oracle as po
 from peregrine_b200 import cuda
 from peregrine_b200.resident import upload_layer
 from peregrine_b200.synth import synth_layer, synth_tokens
-from tests.gpu_common import bits, dev  # noqa: F401
+from tests.gpu_common import bits
 from tests.refmodel import o_expert, oracle_layer_forward, rel_err
 
 pytestmark = pytest.mark.gpu
