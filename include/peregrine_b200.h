@@ -209,6 +209,19 @@ int coli_cuda_moe_layer_read_taps(ColiCudaMoeLayer *layer, int32_t *gateup_taps,
 int coli_cuda_moe_layer_set_profile(ColiCudaMoeLayer *layer, int enable);
 int coli_cuda_moe_layer_profile(ColiCudaMoeLayer *layer, double *stage_ms7, uint64_t *calls);
 
+/* The int4 product of coli_cuda_pipe_gemm for callers that must not allocate.  It has no
+ * counterpart in the reference (cuda/backend_cuda.h has no allocation-free entry).  Same
+ * arguments and result as coli_cuda_pipe_gemm for an int4 tensor (fmt 2 or grouped): y_dev[S,O] =
+ * x_dev[S,I] W^T, device pointers, enqueued on the device's stream.  Its scratch (int8 copy of
+ * x, row scales, block sums, slot table) is a 1 MiB array inside the library image instead
+ * of cudaMalloc'ed buffers, so it calls no cudaMalloc/cudaFree: meant for a decode lane that
+ * runs with VRAM fully committed to experts, or where a device-wide synchronising call is
+ * not allowed.  Requests whose scratch exceeds 1 MiB (about S*I*1.13 bytes; S <= 151 at
+ * I = 6144) are refused with a message.  The first call on a device resolves the array's
+ * address and should come before any stream capture; all calls on a device share the array,
+ * so calls that overlap on the GPU race. */
+int coli_cuda_pipe_gemm_noalloc(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S);
+
 /* Device error word of a context: 0 when no kernel reported a problem since the
  * last call; otherwise the code (1 = a bounded wait on a copy barrier expired). */
 int coli_cuda_last_device_error(int device);

@@ -703,3 +703,4 @@ PGB_EXPORT int coli_cuda_shared_mlp_w4a16(ColiCudaTensor *gate, ColiCudaTensor *
 
 #include "backend_layer.inc"
 #include "backend_pipe.inc"
+#include "backend_noalloc.inc"
