@@ -380,12 +380,12 @@ PGB_EXPORT int coli_cuda_tensor_device(const ColiCudaTensor *tensor) { return te
 
 // ------------------------------------------------------------ GEMV dispatch
 static size_t gemv_xs_bytes(int n_xrows, int kp, int nblk) {
-    return (((size_t)n_xrows * kp + 15) & ~(size_t)15) + (size_t)n_xrows * nblk * 4;
+    return (((size_t)n_xrows * kp + 15) & ~(size_t)15) + (size_t)n_xrows * nblk * 4 + (size_t)n_xrows * 8 + 16;
 }
 
-template <int RMAX, bool GROUPED, int BPG, bool XS>
+template <int RMAX, bool GROUPED, int BPG, int XS, bool TAP>
 static int gemv_launch_t(Ctx *c, const GemvParams &P, size_t smem) {
-    auto kfn = gemv_w4a8_kernel<RMAX, GROUPED, BPG, XS>;
+    auto kfn = gemv_w4a8_kernel<RMAX, GROUPED, BPG, XS, TAP>;
     static std::atomic<uint32_t> configured{0};  // one bit per device slot
     const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
     if (!(configured.load() & bit)) {
@@ -394,44 +394,66 @@ static int gemv_launch_t(Ctx *c, const GemvParams &P, size_t smem) {
             return 0;
         configured.fetch_or(bit);
     }
-    return launch(kfn, dim3(c->sms), dim3(kGemvWarps * 32), smem, c->stream, "w4a8 gemv launch", P);
+    return launch(kfn, dim3(c->sms), dim3(kGemvThreads), smem, c->stream, "w4a8 gemv launch", P);
+}
+
+template <int RMAX, bool GROUPED, int BPG>
+static int gemv_launch_x(Ctx *c, const GemvParams &P, int xs, size_t smem) {
+    // the tap variant is a debugging aid
+    if (P.tap) {
+        if (xs == 2) return gemv_launch_t<RMAX, GROUPED, BPG, 2, true>(c, P, smem);
+        if (xs == 1) return gemv_launch_t<RMAX, GROUPED, BPG, 1, true>(c, P, smem);
+        return gemv_launch_t<RMAX, GROUPED, BPG, 0, true>(c, P, smem);
+    }
+    if (xs == 2) return gemv_launch_t<RMAX, GROUPED, BPG, 2, false>(c, P, smem);
+    if (xs == 1) return gemv_launch_t<RMAX, GROUPED, BPG, 1, false>(c, P, smem);
+    return gemv_launch_t<RMAX, GROUPED, BPG, 0, false>(c, P, smem);
 }
 
 template <int RMAX>
-static int gemv_launch_r(Ctx *c, const GemvParams &P, bool grouped, bool xs, size_t smem) {
-    if (grouped) {
-        if (P.bpg == 1)
-            return xs ? gemv_launch_t<RMAX, true, 1, true>(c, P, smem) : gemv_launch_t<RMAX, true, 1, false>(c, P, smem);
-        return xs ? gemv_launch_t<RMAX, true, 0, true>(c, P, smem) : gemv_launch_t<RMAX, true, 0, false>(c, P, smem);
+static int gemv_launch_r(Ctx *c, const GemvParams &P, bool grouped, int bpg, int xs, size_t smem) {
+    if (!grouped) return gemv_launch_x<RMAX, false, 1>(c, P, xs, smem);
+    switch (bpg) {
+        case 1: return gemv_launch_x<RMAX, true, 1>(c, P, xs, smem);
+        case 2: return gemv_launch_x<RMAX, true, 2>(c, P, xs, smem);
+        case 4: return gemv_launch_x<RMAX, true, 4>(c, P, xs, smem);
+        case 8: return gemv_launch_x<RMAX, true, 8>(c, P, xs, smem);
     }
-    return xs ? gemv_launch_t<RMAX, false, 1, true>(c, P, smem) : gemv_launch_t<RMAX, false, 1, false>(c, P, smem);
+    return fail("w4a8 gemv: unsupported group size");
+}
+
+// True when the launch's activation rows fit in shared memory beside the rings.
+static bool gemv_rows_fit(Ctx *c, int n_xrows, const W4Layout &L) {
+    return (size_t)kRingBytes + kGemvBarBytes + gemv_xs_bytes(n_xrows, L.kp, L.nblk) + 1024 <= c->smem_optin;
 }
 
 // Fills the layout-dependent fields and launches.  `max_rows` bounds the rows of any slot.
-static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_rows) {
+// `want_quant_stage`: the caller filled x_f32 / amax_bits and prefers the kernel to quantise
+// the rows itself; honoured only when the rows fit in shared memory (the return value of
+// gemv_rows_fit tells the caller beforehand).
+static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_rows, bool want_quant_stage = false) {
     P.mode = mode;
-    P.ng = L.ng;
-    P.bpg = L.bpg;
-    P.gpc = L.gpc;
     P.nchunk = L.nchunk;
-    P.group_bytes = L.group_bytes;
+    P.chunk_bytes = L.chunk_bytes;
     P.ntile = L.ntile;
     P.warp_tiles = (mode == 0) ? L.ntile : (L.ntile + 1) / 2;
     P.O = L.O;
+    P.K = L.K;
+    P.ng_tap = L.grouped ? L.ng_src : 1;
     P.tile_bytes = L.tile_bytes;
     P.xq_stride = L.kp;
     P.cs_stride = L.nblk;
     P.err = c->err_dev;
     const size_t base = (size_t)kRingBytes + kGemvBarBytes;
-    const size_t xs_need = gemv_xs_bytes(P.n_xrows, L.kp, L.nblk);
-    const bool xs = base + xs_need + 256 <= c->smem_optin;
-    const size_t smem = base + (xs ? xs_need : 0);
-    if (smem > c->smem_optin) return fail("w4a8 gemv: shared memory budget exceeded");
+    const bool fit = gemv_rows_fit(c, P.n_xrows, L);
+    const int xs = fit ? (want_quant_stage ? 2 : 1) : 0;
+    if (want_quant_stage && !fit) return fail("w4a8 gemv: quantising stage requested but rows do not fit");
+    const size_t smem = base + (fit ? gemv_xs_bytes(P.n_xrows, L.kp, L.nblk) : 0);
     const bool grouped = L.grouped != 0;
-    if (max_rows <= 1) return gemv_launch_r<1>(c, P, grouped, xs, smem);
-    if (max_rows <= 2) return gemv_launch_r<2>(c, P, grouped, xs, smem);
-    if (max_rows <= 4) return gemv_launch_r<4>(c, P, grouped, xs, smem);
-    return gemv_launch_r<8>(c, P, grouped, xs, smem);
+    if (max_rows <= 1) return gemv_launch_r<1>(c, P, grouped, L.bpg, xs, smem);
+    if (max_rows <= 2) return gemv_launch_r<2>(c, P, grouped, L.bpg, xs, smem);
+    if (max_rows <= 4) return gemv_launch_r<4>(c, P, grouped, L.bpg, xs, smem);
+    return gemv_launch_r<8>(c, P, grouped, L.bpg, xs, smem);
 }
 
 static int qrow_run(Ctx *c, const float *x, long long ldx, int K, const W4Layout &L, int8_t *xq, float *sx, int *cs,

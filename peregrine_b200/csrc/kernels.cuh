@@ -21,6 +21,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -112,11 +115,21 @@ __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ 
 }
 
 // ------------------------------------------------------------ int4 x int8 GEMV
-constexpr int kGemvWarps = 8;
-constexpr int kGemvStages = 4;
-constexpr int kStageBytes = 2 * kChunkMaxBytes;
+constexpr int kGemvWarps = 12;
+constexpr int kGemvStages = 3;
+constexpr int kGemvThreads = kGemvWarps * 32;
+constexpr int kStageBytes = 2 * kChunkMaxBytes;  // two half-warp chunks
 constexpr int kRingBytes = kGemvWarps * kGemvStages * kStageBytes;
-constexpr int kGemvBarBytes = kGemvWarps * kGemvStages * 8;
+constexpr int kGemvBarBytes = ((kGemvWarps * kGemvStages * 8 + 127) / 128) * 128;
+
+// Bounded wait on an mbarrier phase; false after ~2e9 cycles.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > 2000000000LL) return false;
+    return true;
+}
 
 // One expert's share of a launch.
 struct GemvSlot {
@@ -128,22 +141,43 @@ struct GemvSlot {
     int nrows;  // pair rows of this expert
 };
 
+// The ordered combine a down launch can finish with (device-resident layer only).
+struct CombineArgs {
+    int *col_done;           // [warp_tiles] arrival counters, zero at launch (nullptr: no fused combine)
+    const int *keff;         // [M]
+    const int *comb_pair;    // [M*k] pair rows of token s in batch-union order
+    const float *comb_w;     // [M*k] their gate weights
+    const int *shared_pair0; // [1] first pair row of the shared expert, -1 if none
+    float *out;              // [M, D]
+    long long ldo;
+    int M, k;
+};
+
 struct GemvParams {
     const GemvSlot *slots;
     const int *n_slots;  // device scalar
     int mode;            // 0: gate/up + SwiGLU -> h ; 1: down -> y
-    int ng, bpg, gpc, nchunk, group_bytes, ntile, warp_tiles, O;
+    int nchunk, chunk_bytes, ntile, warp_tiles, O;
+    int ng_tap;          // groups per row in the tap layout (ceil(K/gs); 1 for per-row scales)
     unsigned long long tile_bytes;
-    const int8_t *xq;  // activation rows, int8, natural element order
+    const int8_t *xq;  // activation rows, int8, natural element order, padded to nchunk*256
     int xq_stride;     // bytes per activation row (= kp)
     const int *csum;   // -8*sum per 32-block
     int cs_stride;     // ints per activation row (= nblk)
     const float *sx;   // activation row scales
     const int *rowmap; // activation row of pair p (nullptr: p itself)
     int n_xrows;       // activation rows staged in shared memory (XS kernels)
+    // QS kernels quantise the activation rows themselves while staging them:
+    const float *x_f32;   // [n_xrows, K] fp32 rows (row stride x_ld)
+    long long x_ld;
+    int K;                // logical row length
+    const unsigned *amax_bits;  // [n_xrows] bit pattern of max|x| per row
+    const int *n_xrows_dev;     // rows actually valid (device scalar; nullptr: n_xrows)
+    unsigned *amax_out;   // mode 0: per pair row, atomicMax of |h| bits (nullptr: off)
     float *out;
     long long out_stride;
-    int *tap;  // optional per-block int32 accumulators [pair][O][ng]
+    CombineArgs comb;
+    int *tap;  // optional per-group int32 accumulators (TAP kernels)
     int *err;
 };
 
@@ -191,17 +225,27 @@ __device__ __forceinline__ void cursor_next(TileCursor &c, const GemvParams &P, 
 }
 
 // Each warp streams two 16-row tiles (lanes 0-15 / 16-31) through a private
-// ring of kGemvStages shared-memory stages filled by bulk copies; lane L owns
-// one weight row for the whole K extent, so the fp32 fold over groups runs in
-// ascending group order exactly as crates/peregrine-kernels/src/idot.rs:98-110
-// and matmul.rs:93-106 (grouped) / :75-87 (per-row scale) prescribe.
+// ring of kGemvStages shared-memory stages filled by bulk copies of one
+// 256-element chunk each; lane L owns one weight row for the whole K extent, so
+// the fp32 fold over groups runs in ascending group order exactly as
+// crates/peregrine-kernels/src/idot.rs:98-110 and matmul.rs:93-106 (grouped) /
+// :75-87 (per-row scale) prescribe.
 //   mode 0: half 0 = gate tile t, half 1 = up tile t; epilogue
 //           h = silu(g) * u (crates/peregrine-model/src/math.rs:108-118)
 //   mode 1: halves = down tiles 2t, 2t+1; epilogue y = acc * sx
 // RMAX activation rows are processed per pass over a tile; an expert with more
-// rows re-streams its tile (from L2) once per extra pass.
-template <int RMAX, bool GROUPED, int BPG, bool XS>
-__global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const GemvParams P) {
+// rows re-streams its tile (from L2) once per extra pass.  BPG = 32-element
+// blocks per scale group (gs/32); a chunk always holds 8 blocks, so the inner
+// loops have constant trip counts and fold into immediates.
+//   XS = 0: activation rows are read from global memory (read-only path)
+//   XS = 1: the launch's int8 rows are first copied into shared memory
+//   XS = 2: the launch's fp32 rows are quantised into shared memory by the CTA
+//           itself (crates/peregrine-kernels/src/quant.rs:14-33) from a row
+//           maximum the producing launch left in amax_bits
+template <int RMAX, bool GROUPED, int BPG, int XS, bool TAP>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvParams P) {
+    constexpr int GPC = kChunkBlocks / BPG;
+    constexpr int CHUNK_BYTES = kChunkSlabBytes + (GROUPED ? GPC * 64 : 0);
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = lane >> 4, r16 = lane & 15;
@@ -211,6 +255,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const Gem
     int8_t *xs = reinterpret_cast<int8_t *>(smem + kRingBytes + kGemvBarBytes);
     const int xs_bytes = (P.n_xrows * P.xq_stride + 15) & ~15;
     int *cs_s = reinterpret_cast<int *>(xs + xs_bytes);
+    float *sx_s = reinterpret_cast<float *>(cs_s + P.n_xrows * P.cs_stride);
 
     if (lane == 0) {
         for (int s = 0; s < kGemvStages; ++s) mbar_init(bar_u32 + s * 8, 1);
@@ -219,10 +264,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const Gem
     }
     __syncwarp();
 
-    const int bpg = (BPG > 0) ? BPG : P.bpg;
-    const int group_bytes = bpg * kSlabBytes + (GROUPED ? kScaleBytes : 0);
-    const int half_off = P.gpc * group_bytes;
-    const int total = (*P.n_slots) * P.warp_tiles;
+    const int n_slots = *P.n_slots;
+    const int total = n_slots * P.warp_tiles;
     const int stride = gridDim.x * kGemvWarps;
 
     TileCursor fc, cc;
@@ -234,16 +277,13 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const Gem
     uint32_t fq = 0, cq = 0;
 
     auto issue = [&](const TileCursor &c, uint32_t q) {
-        const int g0 = c.chunk * P.gpc;
-        const int ngc = min(P.gpc, P.ng - g0);
-        const uint32_t bytes = (uint32_t)(ngc * group_bytes);
         const uint32_t stage = q % kGemvStages;
         const uint32_t bar = bar_u32 + stage * 8;
         const uint32_t dst = ring_u32 + stage * kStageBytes;
-        const size_t off = (size_t)g0 * group_bytes;
-        mbar_expect_tx(bar, c.b ? 2 * bytes : bytes);
-        bulk_g2s(dst, c.a + off, bytes, bar);
-        if (c.b) bulk_g2s(dst + half_off, c.b + off, bytes, bar);
+        const size_t off = (size_t)c.chunk * CHUNK_BYTES;
+        mbar_expect_tx(bar, c.b ? 2 * CHUNK_BYTES : CHUNK_BYTES);
+        bulk_g2s(dst, c.a + off, CHUNK_BYTES, bar);
+        if (c.b) bulk_g2s(dst + kChunkMaxBytes, c.b + off, CHUNK_BYTES, bar);
     };
 
     // first fill of the ring overlaps the activation staging below
@@ -253,17 +293,81 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const Gem
         ++fq;
     }
 
-    if (XS) {
+    if (XS == 1) {
         const int n16 = xs_bytes >> 4;
         const uint4 *src = reinterpret_cast<const uint4 *>(P.xq);
         uint4 *dst = reinterpret_cast<uint4 *>(xs);
         for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
         const int ncs = P.n_xrows * P.cs_stride;
         for (int i = threadIdx.x; i < ncs; i += blockDim.x) cs_s[i] = P.csum[i];
+        for (int i = threadIdx.x; i < P.n_xrows; i += blockDim.x) sx_s[i] = P.sx[i];
+        __syncthreads();
+    } else if (XS == 2) {
+        const int nrows_valid = P.n_xrows_dev ? min(*P.n_xrows_dev, P.n_xrows) : P.n_xrows;
+        float *inv_s = sx_s + P.n_xrows;  // scratch: 1/s per row
+        for (int row = threadIdx.x; row < nrows_valid; row += blockDim.x) {
+            float s = __fdiv_rn(__uint_as_float(P.amax_bits[row]), 127.0f);
+            if (s < 1e-12f) s = 1e-12f;
+            sx_s[row] = s;
+            inv_s[row] = __fdiv_rn(1.0f, s);
+        }
+        __syncthreads();
+        // four consecutive elements per thread and step; eight neighbouring lanes cover one
+        // 32-element block, so the block sum is three shuffles.  Loads of a whole step batch are
+        // issued before any of them is used.
+        const int q4_per_row = P.xq_stride >> 2;
+        const int total4 = nrows_valid * q4_per_row;
+        const bool vec_ok = ((P.x_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(P.x_f32) & 15) == 0);
+        constexpr int kBatch = 4;
+        for (int base4 = 0; base4 < total4; base4 += kBatch * kGemvThreads) {
+            float4 v[kBatch];
+            int rowv[kBatch], c4v[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int i4 = base4 + u * kGemvThreads + (int)threadIdx.x;
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                rowv[u] = -1;
+                c4v[u] = 0;
+                if (i4 < total4) {
+                    const int row = i4 / q4_per_row, c4 = i4 - row * q4_per_row;
+                    rowv[u] = row;
+                    c4v[u] = c4;
+                    const float *src = P.x_f32 + (long long)row * P.x_ld + 4 * c4;
+                    if (vec_ok && 4 * c4 + 3 < P.K) {
+                        v[u] = __ldcg(reinterpret_cast<const float4 *>(src));
+                    } else {
+                        if (4 * c4 + 0 < P.K) v[u].x = __ldcg(src + 0);
+                        if (4 * c4 + 1 < P.K) v[u].y = __ldcg(src + 1);
+                        if (4 * c4 + 2 < P.K) v[u].z = __ldcg(src + 2);
+                        if (4 * c4 + 3 < P.K) v[u].w = __ldcg(src + 3);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                // all 32 lanes take part in the shuffles; lanes past the end carry zeros
+                const float inv = rowv[u] >= 0 ? inv_s[rowv[u]] : 0.0f;
+                const int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].x, inv))));
+                const int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].y, inv))));
+                const int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].z, inv))));
+                const int q3 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].w, inv))));
+                int sum = q0 + q1 + q2 + q3;
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                if (rowv[u] >= 0) {
+                    const uint32_t packed = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) |
+                                            ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+                    *reinterpret_cast<uint32_t *>(xs + (size_t)rowv[u] * P.xq_stride + 4 * c4v[u]) = packed;
+                    if ((c4v[u] & 7) == 0) cs_s[rowv[u] * P.cs_stride + (c4v[u] >> 3)] = -8 * sum;
+                }
+            }
+        }
         __syncthreads();
     }
     const int8_t *xbase = XS ? xs : P.xq;
     const int *csbase = XS ? cs_s : P.csum;
+    const float *sxbase = XS ? sx_s : P.sx;
 
     float acc[RMAX];
     int iacc[RMAX];
@@ -272,7 +376,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const Gem
 
     while (cc.i < total) {
         // keep the ring full: the stage being refilled was consumed one iteration ago
-        while (fc.i < total && fq < cq + kGemvStages) {
+        if (fc.i < total && fq < cq + kGemvStages) {
             if (lane == 0) {
                 fence_proxy_async();
                 issue(fc, fq);
@@ -283,15 +387,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const Gem
         const uint32_t stage = cq % kGemvStages;
         const uint32_t parity = (cq / kGemvStages) & 1u;
         {
-            // bounded wait: give up after ~2e9 cycles, flag the error and leave
-            uint32_t done = mbar_try_wait(bar_u32 + stage * 8, parity);
-            if (!done) {
-                const long long t0 = clock64();
-                while (!(done = mbar_try_wait(bar_u32 + stage * 8, parity))) {
-                    if (clock64() - t0 > 2000000000LL) break;
-                }
-            }
-            if (__any_sync(0xffffffffu, !done)) {
+            const bool ok = mbar_wait_bounded(bar_u32 + stage * 8, parity);
+            if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) atomicExch(P.err, kErrBarrierTimeout);
                 failed = true;
                 break;
@@ -307,69 +404,84 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const Gem
                 arow[r] = P.rowmap ? P.rowmap[p] : p;
             }
         }
-        const int g0 = cc.chunk * P.gpc;
-        const int ngc = min(P.gpc, P.ng - g0);
-        const uint8_t *sbase = ring + stage * kStageBytes + half * half_off + r16 * 16;
+        const uint8_t *wp = ring + stage * kStageBytes + half * kChunkMaxBytes + r16 * 16;
         const int o_half = (P.mode == 0) ? (cc.tile * 16 + r16) : (cc.tile * 32 + lane);
-#pragma unroll 2
-        for (int gi = 0; gi < ngc; ++gi) {
-            const uint8_t *gp = sbase + gi * group_bytes;
-            int dsum[RMAX];
+
+        float sc[GPC];
+        if (GROUPED) {
+            const float *sp =
+                reinterpret_cast<const float *>(ring + stage * kStageBytes + half * kChunkMaxBytes + kChunkSlabBytes) +
+                r16 * GPC;
+            if constexpr (GPC >= 4) {
 #pragma unroll
-            for (int r = 0; r < RMAX; ++r) dsum[r] = 0;
-#pragma unroll
-            for (int b = 0; b < bpg; ++b) {
-                const uint4 wv = *reinterpret_cast<const uint4 *>(gp + b * kSlabBytes);
-                const int kb = (g0 + gi) * bpg + b;
-                const uint32_t l0 = wv.x & 0x0F0F0F0Fu, l1 = wv.y & 0x0F0F0F0Fu, l2 = wv.z & 0x0F0F0F0Fu,
-                               l3 = wv.w & 0x0F0F0F0Fu;
-                const uint32_t h0 = wv.x & 0xF0F0F0F0u, h1 = wv.y & 0xF0F0F0F0u, h2 = wv.z & 0xF0F0F0F0u,
-                               h3 = wv.w & 0xF0F0F0F0u;
-#pragma unroll
-                for (int r = 0; r < RMAX; ++r) {
-                    const int8_t *xr = xbase + (size_t)arow[r] * P.xq_stride + kb * 32;
-                    uint4 x0, x1;
-                    int lo;
-                    if (XS) {
-                        x0 = *reinterpret_cast<const uint4 *>(xr);
-                        x1 = *reinterpret_cast<const uint4 *>(xr + 16);
-                        lo = csbase[arow[r] * P.cs_stride + kb];
-                    } else {
-                        x0 = __ldg(reinterpret_cast<const uint4 *>(xr));
-                        x1 = __ldg(reinterpret_cast<const uint4 *>(xr + 16));
-                        lo = __ldg(csbase + (size_t)arow[r] * P.cs_stride + kb);
-                    }
-                    lo = dp4a_us(l0, x0.x, lo);
-                    lo = dp4a_us(l1, x0.y, lo);
-                    lo = dp4a_us(l2, x0.z, lo);
-                    lo = dp4a_us(l3, x0.w, lo);
-                    int hi = dp4a_us(h0, x1.x, 0);
-                    hi = dp4a_us(h1, x1.y, hi);
-                    hi = dp4a_us(h2, x1.z, hi);
-                    hi = dp4a_us(h3, x1.w, hi);
-                    dsum[r] += lo + (hi >> 4);  // hi is exactly 16x the upper-half dot
+                for (int j = 0; j < GPC / 4; ++j) {
+                    const float4 v = *reinterpret_cast<const float4 *>(sp + 4 * j);
+                    sc[4 * j + 0] = v.x;
+                    sc[4 * j + 1] = v.y;
+                    sc[4 * j + 2] = v.z;
+                    sc[4 * j + 3] = v.w;
                 }
+            } else {
+#pragma unroll
+                for (int j = 0; j < GPC; ++j) sc[j] = sp[j];
             }
-            if (GROUPED) {
-                const float sc = *reinterpret_cast<const float *>(gp - r16 * 16 + bpg * kSlabBytes + r16 * 4);
+        }
 #pragma unroll
-                for (int r = 0; r < RMAX; ++r) acc[r] = __fadd_rn(acc[r], __fmul_rn(sc, (float)dsum[r]));
-                if (P.tap != nullptr && o_half < P.O && (P.mode == 1 || true)) {
+        for (int r = 0; r < RMAX; ++r) {
+            // one activation row at a time keeps the live register set small
+            const int8_t *xr = xbase + (size_t)arow[r] * P.xq_stride + cc.chunk * kChunkElems;
+            const int *cp = csbase + (size_t)arow[r] * P.cs_stride + cc.chunk * kChunkBlocks;
+            int4 c0, c1;
+            if (XS) {
+                c0 = *reinterpret_cast<const int4 *>(cp);
+                c1 = *reinterpret_cast<const int4 *>(cp + 4);
+            } else {
+                c0 = __ldg(reinterpret_cast<const int4 *>(cp));
+                c1 = __ldg(reinterpret_cast<const int4 *>(cp + 4));
+            }
+            const int cs[kChunkBlocks] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-                    for (int r = 0; r < RMAX; ++r) {
+            for (int gi = 0; gi < GPC; ++gi) {
+                int dsum = 0;
+#pragma unroll
+                for (int b = 0; b < BPG; ++b) {
+                    const int blk = gi * BPG + b;
+                    const uint4 wv = *reinterpret_cast<const uint4 *>(wp + blk * kSlabBytes);
+                    uint4 x0, x1;
+                    if (XS) {
+                        x0 = *reinterpret_cast<const uint4 *>(xr + blk * 32);
+                        x1 = *reinterpret_cast<const uint4 *>(xr + blk * 32 + 16);
+                    } else {
+                        x0 = __ldg(reinterpret_cast<const uint4 *>(xr + blk * 32));
+                        x1 = __ldg(reinterpret_cast<const uint4 *>(xr + blk * 32 + 16));
+                    }
+                    int lo = cs[blk];
+                    lo = dp4a_us(wv.x & 0x0F0F0F0Fu, x0.x, lo);
+                    lo = dp4a_us(wv.y & 0x0F0F0F0Fu, x0.y, lo);
+                    lo = dp4a_us(wv.z & 0x0F0F0F0Fu, x0.z, lo);
+                    lo = dp4a_us(wv.w & 0x0F0F0F0Fu, x0.w, lo);
+                    int hi = dp4a_us(wv.x & 0xF0F0F0F0u, x1.x, 0);
+                    hi = dp4a_us(wv.y & 0xF0F0F0F0u, x1.y, hi);
+                    hi = dp4a_us(wv.z & 0xF0F0F0F0u, x1.z, hi);
+                    hi = dp4a_us(wv.w & 0xF0F0F0F0u, x1.w, hi);
+                    dsum += lo + (hi >> 4);  // hi is exactly 16x the upper-half dot
+                }
+                if (GROUPED) {
+                    acc[r] = __fadd_rn(acc[r], __fmul_rn(sc[gi], (float)dsum));
+                    if (TAP) {
+                        const int g = cc.chunk * GPC + gi;
                         const int ridx = cc.pass * RMAX + r;
-                        if (ridx < cc.nrows) {
+                        if (P.tap != nullptr && o_half < P.O && g < P.ng_tap && ridx < cc.nrows) {
                             // mode 0 taps gate (half 0) and up (half 1) side by side: [pair][2][O][ng]
                             const long long base =
                                 (P.mode == 0) ? ((long long)(cc.row0 + ridx) * 2 + half) * P.O + o_half
                                               : (long long)(cc.row0 + ridx) * P.O + o_half;
-                            P.tap[base * P.ng + (g0 + gi)] = dsum[r];
+                            P.tap[base * P.ng_tap + g] = dsum;
                         }
                     }
+                } else {
+                    iacc[r] += dsum;
                 }
-            } else {
-#pragma unroll
-                for (int r = 0; r < RMAX; ++r) iacc[r] += dsum[r];
             }
         }
         __syncwarp();
@@ -383,12 +495,12 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const Gem
             for (int r = 0; r < RMAX; ++r) {
                 const int ridx = cc.pass * RMAX + r;
                 const bool valid = ridx < cc.nrows;
-                const float sxa = P.sx[arow[r]];
+                const float sxa = sxbase[arow[r]];
                 float v;
                 if (GROUPED) {
                     v = __fmul_rn(acc[r], sxa);
                 } else {
-                    if (P.tap != nullptr && valid && o_half < P.O) {
+                    if (TAP && P.tap != nullptr && valid && o_half < P.O) {
                         const long long base = (P.mode == 0) ? ((long long)(cc.row0 + ridx) * 2 + half) * P.O + o_half
                                                              : (long long)(cc.row0 + ridx) * P.O + o_half;
                         P.tap[base] = iacc[r];
@@ -397,10 +509,50 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_w4a8_kernel(const Gem
                 }
                 if (P.mode == 0) {
                     const float u = __shfl_down_sync(0xffffffffu, v, 16);
-                    if (valid && half == 0 && o_half < P.O)
-                        P.out[(long long)(cc.row0 + ridx) * P.out_stride + o_half] = __fmul_rn(silu32(v), u);
+                    float hval = 0.0f;
+                    const bool store = valid && half == 0 && o_half < P.O;
+                    if (store) {
+                        hval = __fmul_rn(silu32(v), u);
+                        P.out[(long long)(cc.row0 + ridx) * P.out_stride + o_half] = hval;
+                    }
+                    if (P.amax_out != nullptr) {
+                        // row maximum of |h| for the quantiser of the next launch: max is order-free,
+                        // NaN never becomes the maximum (crates/peregrine-kernels/src/quant.rs:17-22)
+                        float a = fabsf(hval);
+                        if (!(a == a)) a = 0.0f;
+                        for (int o = 8; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+                        if (valid && lane == 0 && a > 0.0f) atomicMax(P.amax_out + cc.row0 + ridx, __float_as_uint(a));
+                    }
                 } else {
                     if (valid && o_half < P.O) P.out[(long long)(cc.row0 + ridx) * P.out_stride + o_half] = v;
+                }
+            }
+            if (P.mode == 1 && P.comb.col_done != nullptr && cc.pass == cc.npass - 1) {
+                // Ordered combine by the warp that completes an output column tile: out starts at
+                // zero, each expert's row is added as out + (w * y) in batch-union order, the shared
+                // expert last (crates/peregrine-model/src/mlp.rs:111-127, concurrent.rs:1866-1929).
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) last = (atomicAdd(P.comb.col_done + cc.tile, 1) == n_slots - 1);
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    const int col = cc.tile * 32 + lane;
+                    const int sp0 = *P.comb.shared_pair0;
+                    if (col < P.O) {
+                        for (int s = 0; s < P.comb.M; ++s) {
+                            const int ke = P.comb.keff[s];
+                            float a = 0.0f;
+                            for (int j = 0; j < ke; ++j) {
+                                const int p = P.comb.comb_pair[s * P.comb.k + j];
+                                const float wgt = P.comb.comb_w[s * P.comb.k + j];
+                                a = __fadd_rn(a, __fmul_rn(wgt, __ldcg(P.out + (long long)p * P.out_stride + col)));
+                            }
+                            if (sp0 >= 0) a = __fadd_rn(a, __ldcg(P.out + (long long)(sp0 + s) * P.out_stride + col));
+                            P.comb.out[(long long)s * P.comb.ldo + col] = a;
+                        }
+                    }
                 }
             }
         }
@@ -538,10 +690,16 @@ struct RoutePlan {
     int *union_ids;   // [E]   expert id of routed slot p (batch-union order)
     int *pair_token;  // [P]   token of pair p (the GEMV rowmap for gate/up)
     int *tok_pair;    // [M*k] pair index of (s, kk)
-    int *tok_order;   // [M*k] kk values of token s sorted by union position
+    int *comb_pair;   // [M*k] pair rows of token s in batch-union order (keff[s] entries)
+    float *comb_w;    // [M*k] gate weights in the same order
     int *shared_pair0;  // [1] first pair of the shared expert (pairs s.. in token order), -1 if none
     GemvSlot *gu_slots;  // [E+1]
     GemvSlot *dn_slots;  // [E+1]
+    // per-step scratch the plan clears for the launches that follow it
+    int *col_done;      // [n_col] column-tile arrival counters of the down launch
+    int n_col;
+    unsigned *amax;     // [n_amax] row maxima of |h| filled by the gate/up launch
+    int n_amax;
 };
 
 // Per-expert device pointers, indexed by expert id; entry E is the shared expert.
@@ -550,19 +708,26 @@ struct ExpertDev {
     const float *gate_rs, *up_rs, *down_rs;
 };
 
-// Top-k selection, batch union and the pair layout, one CTA.
+constexpr int kPlanCacheTokens = 64;  // routing of up to this many tokens is kept in shared memory
+__host__ __device__ inline size_t route_plan_smem_bytes(int E, int nwarp, int k) {
+    // sig/choice per warp, first_seen, cnt, slot_of, row0 (E+2), base, mask (8E), union (E), nunion,
+    // cached idx / w / keff
+    return (size_t)(2 * nwarp * E + 13 * E + 8 + E) * 4 + (size_t)kPlanCacheTokens * (2 * k + 1) * 4 + 64;
+}
+
+// Top-k selection, batch union and the pair layout, executed by one CTA.
 //   selection: crates/peregrine-model/src/router.rs:86-150 (sigmoid scores, bias
 //     only for choosing, strict '>' from -inf so ties go to the lowest index and
 //     NaN / -inf scores are never chosen, norm over all k slots + 1e-20, scale)
 //   union order: router.rs:420-430 (first seen, s ascending then kk ascending)
 //   rows of an expert: ascending s (crates/peregrine-model/src/mlp.rs:83-95)
 // Pairs are laid out expert by expert in union order, the shared expert last.
-__global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict__ logits,
-                                                         const float *__restrict__ bias, int M, int E, int k,
-                                                         int norm_topk, float routed_scale, int has_shared,
-                                                         const ExpertDev *__restrict__ experts, RoutePlan plan) {
-    extern __shared__ __align__(16) unsigned char rp_smem[];
-    // layout: per-warp sig[E], choice[E]; then first_seen[E], cnt[E], slot_of[E], row0[E+1], base[E], mask[E*8]
+// Routing of the first kPlanCacheTokens tokens is mirrored in shared memory so a
+// decode-sized batch never waits on its own global writes.
+__device__ __forceinline__ void route_plan_body(const float *__restrict__ logits, const float *__restrict__ bias,
+                                                int M, int E, int k, int norm_topk, float routed_scale,
+                                                int has_shared, const ExpertDev *__restrict__ experts,
+                                                const RoutePlan &plan, unsigned char *rp_smem) {
     const int nwarp = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float *sig_all = reinterpret_cast<float *>(rp_smem);
@@ -573,18 +738,33 @@ __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict
     int *row0 = slot_of + E;  // E + 2 entries
     int *base = row0 + E + 2;
     unsigned *mask = reinterpret_cast<unsigned *>(base + E);  // E * 8 words: 256 tokens per sweep
-    __shared__ int s_nunion;
+    int *union_s = reinterpret_cast<int *>(mask + E * 8);     // E
+    int *s_nunion = union_s + E;                              // 1 (+7 pad)
+    int *idx_c = s_nunion + 8;                                // kPlanCacheTokens * k
+    float *w_c = reinterpret_cast<float *>(idx_c + kPlanCacheTokens * k);
+    int *keff_c = reinterpret_cast<int *>(w_c + kPlanCacheTokens * k);
+    const bool cached = M <= kPlanCacheTokens;
+    auto ld_idx = [&](int q) { return cached ? idx_c[q] : plan.idx[q]; };
+    auto ld_w = [&](int q) { return cached ? w_c[q] : plan.w[q]; };
+    auto ld_keff = [&](int s) { return cached ? keff_c[s] : plan.keff[s]; };
+
+    // clear the per-step scratch of the launches that follow
+    for (int i = threadIdx.x; i < plan.n_col; i += blockDim.x) plan.col_done[i] = 0;
+    for (int i = threadIdx.x; i < plan.n_amax; i += blockDim.x) plan.amax[i] = 0u;
 
     // ---- 1. per-token selection, one warp per token
     float *sig = sig_all + warp * E, *choice = choice_all + warp * E;
     for (int s = warp; s < M; s += nwarp) {
         for (int e = lane; e < E; e += 32) {
-            const float sg = sigmoid32(logits[(long long)s * E + e]);
+            const float sg = sigmoid32(__ldcg(logits + (long long)s * E + e));
             sig[e] = sg;
             choice[e] = __fadd_rn(sg, bias[e]);
         }
         __syncwarp();
         int kept = k;
+        // lane kk keeps the kk-th selection of this token (k <= 32)
+        int my_idx = 0;
+        float my_w = 0.0f;
         for (int kk = 0; kk < k; ++kk) {
             float bv = -INFINITY;
             int best = -1;
@@ -608,26 +788,33 @@ __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict
                 kept = kk;
                 break;
             }
-            if (lane == 0) {
-                plan.idx[s * k + kk] = best;
-                plan.w[s * k + kk] = sig[best];
-                choice[best] = -INFINITY;  // never chosen again
+            if (lane == kk) {
+                my_idx = best;
+                my_w = sig[best];
             }
             __syncwarp();
+            if (lane == 0) choice[best] = -INFINITY;  // never chosen again
+            __syncwarp();
+        }
+        // slots >= kept hold expert 0 with weight 0 (my_idx / my_w initial values)
+        if (norm_topk) {
+            float sm = 0.0f;
+            for (int j = 0; j < k; ++j) sm = __fadd_rn(sm, __shfl_sync(0xffffffffu, my_w, j));
+            sm = __fadd_rn(sm, 1e-20f);
+            my_w = __fdiv_rn(my_w, sm);
+        }
+        my_w = __fmul_rn(my_w, routed_scale);
+        if (lane < k) {
+            plan.idx[s * k + lane] = my_idx;
+            plan.w[s * k + lane] = my_w;
+            if (cached) {
+                idx_c[s * k + lane] = my_idx;
+                w_c[s * k + lane] = my_w;
+            }
         }
         if (lane == 0) {
-            for (int slot = kept; slot < k; ++slot) {
-                plan.idx[s * k + slot] = 0;
-                plan.w[s * k + slot] = 0.0f;
-            }
             plan.keff[s] = kept;
-            if (norm_topk) {
-                float sm = 0.0f;
-                for (int j = 0; j < k; ++j) sm = __fadd_rn(sm, plan.w[s * k + j]);
-                sm = __fadd_rn(sm, 1e-20f);
-                for (int j = 0; j < k; ++j) plan.w[s * k + j] = __fdiv_rn(plan.w[s * k + j], sm);
-            }
-            for (int j = 0; j < k; ++j) plan.w[s * k + j] = __fmul_rn(plan.w[s * k + j], routed_scale);
+            if (cached) keff_c[s] = kept;
         }
         __syncwarp();
     }
@@ -636,13 +823,14 @@ __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict
         cnt[e] = 0;
         base[e] = 0;
     }
+    if (threadIdx.x == 0) *s_nunion = 0;
     __syncthreads();
 
     // ---- 2. first-seen key and row count per expert
     for (int q = threadIdx.x; q < M * k; q += blockDim.x) {
         const int s = q / k, kk = q - s * k;
-        if (kk < plan.keff[s]) {
-            const int e = plan.idx[q];
+        if (kk < ld_keff(s)) {
+            const int e = ld_idx(q);
             atomicMin(&first_seen[e], q);
             atomicAdd(&cnt[e], 1);
         }
@@ -650,27 +838,26 @@ __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict
     __syncthreads();
 
     // ---- 3. union position of each routed expert = rank of its first-seen key
-    if (threadIdx.x == 0) s_nunion = 0;
-    __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int pos = -1;
         if (cnt[e] > 0) {
             pos = 0;
             const int key = first_seen[e];
             for (int o = 0; o < E; ++o) pos += (first_seen[o] < key) ? 1 : 0;
+            union_s[pos] = e;
             plan.union_ids[pos] = e;
-            atomicAdd(&s_nunion, 1);
+            atomicAdd(s_nunion, 1);
         }
         slot_of[e] = pos;
     }
     __syncthreads();
-    const int nunion = s_nunion;
-    // ---- 4. first pair row of each slot (serial scan; at most E entries)
+    const int nunion = *s_nunion;
+    // ---- 4. first pair row of each slot (serial scan; at most E entries, all in shared memory)
     if (threadIdx.x == 0) {
         int run = 0;
         for (int p = 0; p < nunion; ++p) {
             row0[p] = run;
-            run += cnt[plan.union_ids[p]];
+            run += cnt[union_s[p]];
         }
         row0[nunion] = run;  // routed pairs
         *plan.n_union = nunion;
@@ -688,14 +875,14 @@ __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict
         for (int i = threadIdx.x; i < E * 8; i += blockDim.x) mask[i] = 0u;
         __syncthreads();
         const int s = sweep0 + threadIdx.x;
-        const int ke = (s < M && threadIdx.x < 256) ? plan.keff[s] : 0;
+        const int ke = (s < M && threadIdx.x < 256) ? ld_keff(s) : 0;
         for (int kk = 0; kk < ke; ++kk) {
-            const int e = plan.idx[s * k + kk];
+            const int e = ld_idx(s * k + kk);
             atomicOr(&mask[e * 8 + (threadIdx.x >> 5)], 1u << (threadIdx.x & 31));
         }
         __syncthreads();
         for (int kk = 0; kk < ke; ++kk) {
-            const int e = plan.idx[s * k + kk];
+            const int e = ld_idx(s * k + kk);
             int rank = 0;
             const int wi = threadIdx.x >> 5;
             for (int w2 = 0; w2 < wi; ++w2) rank += __popc(mask[e * 8 + w2]);
@@ -703,6 +890,15 @@ __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict
             const int p = row0[slot_of[e]] + base[e] + rank;
             plan.pair_token[p] = s;
             plan.tok_pair[s * k + kk] = p;
+            // combine order of token s: its selections sorted by union position
+            const int key = slot_of[e];
+            int pos = 0;
+            for (int j2 = 0; j2 < ke; ++j2) {
+                const int key2 = slot_of[ld_idx(s * k + j2)];
+                pos += (key2 < key || (key2 == key && j2 < kk)) ? 1 : 0;
+            }
+            plan.comb_pair[s * k + pos] = p;
+            plan.comb_w[s * k + pos] = ld_w(s * k + kk);
         }
         __syncthreads();
         for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -716,30 +912,17 @@ __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict
     if (has_shared)
         for (int s = threadIdx.x; s < M; s += blockDim.x) plan.pair_token[routed_pairs + s] = s;
 
-    // ---- 6. combine order of each token: its kk values sorted by union position
-    for (int s = threadIdx.x; s < M; s += blockDim.x) {
-        const int ke = plan.keff[s];
-        for (int j = 0; j < ke; ++j) {
-            const int key = slot_of[plan.idx[s * k + j]];
-            int pos = 0;
-            for (int j2 = 0; j2 < ke; ++j2) {
-                const int key2 = slot_of[plan.idx[s * k + j2]];
-                pos += (key2 < key || (key2 == key && j2 < j)) ? 1 : 0;
-            }
-            plan.tok_order[s * k + pos] = j;
-        }
-    }
-    // ---- 7. GEMV slot tables
+    // ---- 6. GEMV slot tables
     for (int p = threadIdx.x; p < nunion + (has_shared ? 1 : 0); p += blockDim.x) {
         const bool sh = p >= nunion;
-        const ExpertDev ex = experts[sh ? E : plan.union_ids[p]];
+        const ExpertDev ex = experts[sh ? E : union_s[p]];
         GemvSlot g, d;
         g.a = ex.gate;
         g.b = ex.up;
         g.a_rs = ex.gate_rs;
         g.b_rs = ex.up_rs;
         g.row0 = sh ? routed_pairs : row0[p];
-        g.nrows = sh ? M : cnt[plan.union_ids[p]];
+        g.nrows = sh ? M : cnt[union_s[p]];
         d = g;
         d.a = ex.down;
         d.b = nullptr;
@@ -748,6 +931,193 @@ __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict
         plan.gu_slots[p] = g;
         plan.dn_slots[p] = d;
     }
+}
+
+__global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict__ logits,
+                                                         const float *__restrict__ bias, int M, int E, int k,
+                                                         int norm_topk, float routed_scale, int has_shared,
+                                                         const ExpertDev *__restrict__ experts, RoutePlan plan) {
+    extern __shared__ __align__(16) unsigned char rp_smem[];
+    route_plan_body(logits, bias, M, E, k, norm_topk, routed_scale, has_shared, experts, plan, rp_smem);
+}
+
+// ------------------------------------------------- fused routing kernel
+// One launch does everything the layer needs before the experts run:
+//   chain CTAs (one per 8 experts x up to 32 tokens): the router logits of
+//     crates/peregrine-kernels/src/matmul.rs:18-30 — one strictly sequential,
+//     unfused fp32 chain acc = acc + x[d]*w[e,d] per (token, expert), one thread
+//     per chain — with the operands streamed through a four-stage shared-memory
+//     ring by bulk copies issued from a producer warp;
+//   quantiser CTAs (one per token): the int8 copy of x for the gate/up launch;
+//   the chain CTA that finishes last runs route_plan_body.
+constexpr int kRtEPB = 8, kRtMT = 32, kRtSL = 256, kRtMaxStages = 16;
+constexpr int kRtRowFloats = kRtSL + 4;  // 16-byte skew: rows land on distinct banks
+constexpr int kRtThreads = 288;  // 8 chain warps + 1 producer warp
+constexpr int kRtRingBytes = 160 * 1024;   // the ring uses as many stages as fit here (at most 16)
+constexpr int kRtBarOffset = kRtRingBytes; // barriers and flags follow the ring
+__host__ __device__ inline int route_stage_bytes(int M) { return (kRtEPB + (M < kRtMT ? M : kRtMT)) * kRtRowFloats * 4; }
+__host__ __device__ inline int route_stages(int M) {
+    const int n = kRtRingBytes / route_stage_bytes(M);
+    return n > kRtMaxStages ? kRtMaxStages : n;
+}
+
+struct RouteArgs {
+    const float *x;
+    long long ldx;
+    const float *rw, *bias;
+    int M, D, E, k, norm_topk;
+    float routed_scale;
+    int has_shared;
+    float *logits;
+    unsigned *done_counter;  // zero before the first launch; the last CTA resets it
+    const ExpertDev *experts;
+    RoutePlan plan;
+    int n_chain_ctas;
+    // quantiser role
+    int8_t *xq;
+    float *sx;
+    int *xcs;
+    int kp, nblk;
+    int *err;
+};
+
+__global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs A) {
+    extern __shared__ __align__(128) unsigned char rt_smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if ((int)blockIdx.x >= A.n_chain_ctas) {
+        // ---------------- quantiser role (crates/peregrine-kernels/src/quant.rs:14-33)
+        const int row = blockIdx.x - A.n_chain_ctas;
+        const float *xr = A.x + (long long)row * A.ldx;
+        float *red = reinterpret_cast<float *>(rt_smem);
+        float amax = 0.0f;
+        for (int i = tid; i < A.D; i += blockDim.x) {
+            const float a = fabsf(xr[i]);
+            if (a > amax) amax = a;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, amax, o);
+            if (other > amax) amax = other;
+        }
+        if (lane == 0) red[warp] = amax;
+        __syncthreads();
+        float m = red[0];
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (red[w] > m) m = red[w];
+        float s = __fdiv_rn(m, 127.0f);
+        if (s < 1e-12f) s = 1e-12f;
+        const float inv = __fdiv_rn(1.0f, s);
+        if (tid == 0) A.sx[row] = s;
+        for (int blk = warp; blk < A.nblk; blk += (int)(blockDim.x >> 5)) {
+            const int i = blk * 32 + lane;
+            int q = 0;
+            if (i < A.D) {
+                q = __float2int_rn(__fmul_rn(xr[i], inv));
+                q = max(-128, min(127, q));
+            }
+            A.xq[(long long)row * A.kp + i] = (int8_t)q;
+            int sum = q;
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) A.xcs[(long long)row * A.nblk + blk] = -8 * sum;
+        }
+        return;
+    }
+    // ---------------- chain role
+    const int n_eblk = (A.E + kRtEPB - 1) / kRtEPB;
+    const int eb = blockIdx.x % n_eblk, sb = blockIdx.x / n_eblk;
+    const int e0 = eb * kRtEPB, s0 = sb * kRtMT;
+    const int ne = min(kRtEPB, A.E - e0), ns = min(kRtMT, A.M - s0);
+    const int kRtStages = route_stages(A.M), kRtStageBytes = route_stage_bytes(A.M);
+    const int xrow0 = kRtEPB;  // token rows follow the 8 router rows inside a stage
+    const uint32_t full_u32 = smem_u32(rt_smem + kRtBarOffset);
+    const uint32_t empty_u32 = full_u32 + kRtMaxStages * 8;
+    if (tid == 0) {
+        for (int s = 0; s < kRtStages; ++s) {
+            mbar_init(full_u32 + s * 8, 1);
+            mbar_init(empty_u32 + s * 8, 8);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+    const int nslice = (A.D + kRtSL - 1) / kRtSL;
+    bool failed = false;
+    if (warp == 8) {
+        // producer: one bulk copy per operand row and slice (rows 0..ne-1 router, ne.. tokens)
+        const int rows = ne + ns;
+        for (int i = 0; i < nslice; ++i) {
+            const int st = i % kRtStages;
+            if (i >= kRtStages) {
+                const bool ok = mbar_wait_bounded(empty_u32 + st * 8, ((i / kRtStages) + 1) & 1u);
+                if (__any_sync(0xffffffffu, !ok)) {
+                    failed = true;
+                    break;
+                }
+            }
+            const int d0 = i * kRtSL;
+            const int dlen = min(kRtSL, A.D - d0);
+            if (lane == 0) {
+                fence_proxy_async();
+                mbar_expect_tx(full_u32 + st * 8, (uint32_t)(rows * dlen * 4));
+            }
+            __syncwarp();
+            for (int r = lane; r < rows; r += 32) {
+                const float *src = (r < ne) ? A.rw + (long long)(e0 + r) * A.D + d0
+                                            : A.x + (long long)(s0 + r - ne) * A.ldx + d0;
+                const int dstrow = (r < ne) ? r : (xrow0 + r - ne);
+                bulk_g2s(smem_u32(rt_smem + st * kRtStageBytes + dstrow * kRtRowFloats * 4), src,
+                         (uint32_t)(dlen * 4), full_u32 + st * 8);
+            }
+        }
+    } else {
+        const int el = tid & 7, sl = tid >> 3;
+        const bool chain = (el < ne) && (sl < ns);
+        float acc = 0.0f;
+        for (int i = 0; i < nslice; ++i) {
+            const int st = i % kRtStages;
+            const bool ok = mbar_wait_bounded(full_u32 + st * 8, (i / kRtStages) & 1u);
+            if (__any_sync(0xffffffffu, !ok)) {
+                failed = true;
+                break;
+            }
+            if (chain) {
+                const float *wr = reinterpret_cast<const float *>(rt_smem + st * kRtStageBytes) + el * kRtRowFloats;
+                const float *xr =
+                    reinterpret_cast<const float *>(rt_smem + st * kRtStageBytes) + (xrow0 + sl) * kRtRowFloats;
+                const int dlen = min(kRtSL, A.D - i * kRtSL);
+                if (dlen == kRtSL) {
+#pragma unroll 8
+                    for (int d = 0; d < kRtSL; d += 4) {
+                        const float4 w4 = *reinterpret_cast<const float4 *>(wr + d);
+                        const float4 x4 = *reinterpret_cast<const float4 *>(xr + d);
+                        acc = __fadd_rn(acc, __fmul_rn(x4.x, w4.x));
+                        acc = __fadd_rn(acc, __fmul_rn(x4.y, w4.y));
+                        acc = __fadd_rn(acc, __fmul_rn(x4.z, w4.z));
+                        acc = __fadd_rn(acc, __fmul_rn(x4.w, w4.w));
+                    }
+                } else {
+                    for (int d = 0; d < dlen; ++d) acc = __fadd_rn(acc, __fmul_rn(xr[d], wr[d]));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_u32 + st * 8);
+        }
+        if (chain && !failed) A.logits[(long long)(s0 + sl) * A.E + e0 + el] = acc;
+    }
+    if (failed && lane == 0) atomicExch(A.err, kErrBarrierTimeout);
+    // ---------------- the last chain CTA to finish plans the layer
+    __threadfence();
+    __syncthreads();
+    int *s_last = reinterpret_cast<int *>(rt_smem + kRtBarOffset + 2 * kRtMaxStages * 8);
+    if (tid == 0) {
+        const unsigned old = atomicAdd(A.done_counter, 1u);
+        *s_last = (old == (unsigned)A.n_chain_ctas - 1u);
+        if (*s_last) *A.done_counter = 0u;
+    }
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    route_plan_body(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts, A.plan,
+                    rt_smem);
 }
 
 // Routing-weighted combine, crates/peregrine-model/src/mlp.rs:111-127 and
@@ -762,9 +1132,8 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
     const int ke = plan.keff[s];
     float acc = 0.0f;
     for (int j = 0; j < ke; ++j) {
-        const int kk = plan.tok_order[s * k + j];
-        const int p = plan.tok_pair[s * k + kk];
-        acc = __fadd_rn(acc, __fmul_rn(plan.w[s * k + kk], y[(long long)p * ldy + d]));
+        const int p = plan.comb_pair[s * k + j];
+        acc = __fadd_rn(acc, __fmul_rn(plan.comb_w[s * k + j], y[(long long)p * ldy + d]));
     }
     const int sp0 = *plan.shared_pair0;
     if (sp0 >= 0) acc = __fadd_rn(acc, y[(long long)(sp0 + s) * ldy + d]);

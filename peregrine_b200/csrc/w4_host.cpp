@@ -39,35 +39,32 @@ static inline void repack_block16(const uint8_t *src, uint8_t *dst) {
 
 static void repack_tiles(const W4Layout &L, const uint8_t *q, const float *scales, uint8_t *stream, int t0, int t1) {
     const size_t row_bytes = (size_t)(L.K + 1) / 2;
-    const int ng_src = L.grouped ? L.ng : 0;
     for (int t = t0; t < t1; ++t) {
         uint8_t *tile = stream + (size_t)t * L.tile_bytes;
-        for (int g = 0; g < L.ng; ++g) {
-            for (int b = 0; b < L.bpg; ++b) {
-                const int k0 = (g * L.bpg + b) * kBlockElems;
-                for (int r = 0; r < kTileRows; ++r) {
-                    const int o = t * kTileRows + r;
-                    uint8_t *dst = tile + w4_seg_offset(L, g, b, r);
-                    if (o < L.O && k0 + kBlockElems <= L.K) {
-                        // fast path: 16 source bytes hold elements k0..k0+31 in (even, odd) pairs
-                        const uint8_t *src = q + (size_t)o * row_bytes + (size_t)(k0 >> 1);
-                        repack_block16(src, dst);
-                    } else {
-                        for (int p = 0; p < 16; ++p) {
-                            uint8_t lo = src_nibble(q, row_bytes, L.O, L.K, o, k0 + p);
-                            uint8_t hi = src_nibble(q, row_bytes, L.O, L.K, o, k0 + 16 + p);
-                            dst[p] = (uint8_t)(lo | (hi << 4));
-                        }
+        for (int blk = 0; blk < L.nblk; ++blk) {
+            const int k0 = blk * kBlockElems;
+            for (int r = 0; r < kTileRows; ++r) {
+                const int o = t * kTileRows + r;
+                uint8_t *dst = tile + w4_seg_offset(L, blk, r);
+                if (o < L.O && k0 + kBlockElems <= L.K) {
+                    repack_block16(q + (size_t)o * row_bytes + (size_t)(k0 >> 1), dst);
+                } else {
+                    for (int p = 0; p < 16; ++p) {
+                        uint8_t lo = src_nibble(q, row_bytes, L.O, L.K, o, k0 + p);
+                        uint8_t hi = src_nibble(q, row_bytes, L.O, L.K, o, k0 + 16 + p);
+                        dst[p] = (uint8_t)(lo | (hi << 4));
                     }
                 }
             }
-            if (L.grouped) {
+        }
+        if (L.grouped) {
+            const int ng_pad = L.nchunk * L.gpc;
+            for (int g = 0; g < ng_pad; ++g)
                 for (int r = 0; r < kTileRows; ++r) {
                     const int o = t * kTileRows + r;
-                    float s = (o < L.O) ? scales[(size_t)o * ng_src + g] : 0.0f;
+                    float s = (o < L.O && g < L.ng_src) ? scales[(size_t)o * L.ng_src + g] : 0.0f;
                     std::memcpy(tile + w4_scale_offset(L, g, r), &s, 4);
                 }
-            }
         }
     }
 }
@@ -98,8 +95,7 @@ void w4_repack(const W4Layout &L, const uint8_t *q, const float *scales, uint8_t
 int w4_stream_nibble(const W4Layout &L, const uint8_t *stream, int o, int k) {
     const int t = o / kTileRows, r = o % kTileRows;
     const int blk = k / kBlockElems, e = k % kBlockElems;
-    const int g = blk / L.bpg, b = blk % L.bpg;
-    const uint8_t byte = stream[(size_t)t * L.tile_bytes + w4_seg_offset(L, g, b, r) + (size_t)(e & 15)];
+    const uint8_t byte = stream[(size_t)t * L.tile_bytes + w4_seg_offset(L, blk, r) + (size_t)(e & 15)];
     return (e < 16) ? (byte & 0x0F) : (byte >> 4);
 }
 

@@ -22,8 +22,8 @@ static inline int dp4a_us(uint32_t a, uint32_t b, int c) {
 HC_API int pgb_hc_layout(int O, int K, int grouped, int gs, long long *out) {
     W4Layout L;
     if (!w4_layout_make(&L, O, K, grouped, gs)) return 0;
-    long long v[] = {L.O,   L.K,           L.grouped, L.gs,     L.bpg, L.ng,
-                     L.nblk, L.ntile,      L.group_bytes, L.gpc, L.nchunk, L.kp,
+    long long v[] = {L.O,    L.K,     L.grouped,     L.gs,  L.bpg,    L.ng_src,
+                     L.nblk, L.ntile, L.chunk_bytes, L.gpc, L.nchunk, L.kp,
                      (long long)L.tile_bytes, (long long)L.total_bytes};
     std::memcpy(out, v, sizeof(v));
     return 1;
@@ -73,11 +73,12 @@ HC_API void pgb_hc_qrow(const float *x, int K, int kp, int nblk, int8_t *xq, flo
 
 // y[r, o] for nrows activation rows against one matrix, walking the stream chunk
 // by chunk the way one half-warp of gemv_w4a8_kernel does (mode 1 addressing).
-// tap (may be NULL): [nrows][O][ng] per-group int32 (grouped) or [nrows][O] (per-row).
+// tap (may be NULL): [nrows][O][ng_src] per-group int32 (grouped) or [nrows][O] (per-row).
 HC_API int pgb_hc_walk(const uint8_t *stream, const float *row_scales, int O, int K, int grouped, int gs,
                        const int8_t *xq, const int *csum, const float *sx, int nrows, float *y, int *tap) {
     W4Layout L;
     if (!w4_layout_make(&L, O, K, grouped, gs)) return 0;
+    const int GPC = L.gpc, BPG = L.bpg;
     for (int tile = 0; tile < L.ntile; ++tile) {
         const uint8_t *tbase = stream + (size_t)tile * L.tile_bytes;
         for (int r16 = 0; r16 < kTileRows; ++r16) {
@@ -86,20 +87,20 @@ HC_API int pgb_hc_walk(const uint8_t *stream, const float *row_scales, int O, in
                 float acc = 0.0f;
                 int iacc = 0;
                 for (int chunk = 0; chunk < L.nchunk; ++chunk) {
-                    const int g0 = chunk * L.gpc;
-                    const int ngc = (L.ng - g0 < L.gpc) ? L.ng - g0 : L.gpc;
-                    const uint8_t *sbase = tbase + (size_t)g0 * L.group_bytes + r16 * 16;
-                    for (int gi = 0; gi < ngc; ++gi) {
-                        const uint8_t *gp = sbase + (size_t)gi * L.group_bytes;
+                    const uint8_t *wp = tbase + (size_t)chunk * L.chunk_bytes + r16 * 16;
+                    const float *sp = reinterpret_cast<const float *>(tbase + (size_t)chunk * L.chunk_bytes +
+                                                                      kChunkSlabBytes) + r16 * GPC;
+                    const int8_t *xr = xq + (size_t)r * L.kp + chunk * kChunkElems;
+                    const int *cp = csum + (size_t)r * L.nblk + chunk * kChunkBlocks;
+                    for (int gi = 0; gi < GPC; ++gi) {
                         int dsum = 0;
-                        for (int b = 0; b < L.bpg; ++b) {
-                            uint32_t w[4];
-                            std::memcpy(w, gp + b * kSlabBytes, 16);
-                            const int kb = (g0 + gi) * L.bpg + b;
-                            uint32_t x0[4], x1[4];
-                            std::memcpy(x0, xq + (size_t)r * L.kp + kb * 32, 16);
-                            std::memcpy(x1, xq + (size_t)r * L.kp + kb * 32 + 16, 16);
-                            int lo = csum[(size_t)r * L.nblk + kb], hi = 0;
+                        for (int b = 0; b < BPG; ++b) {
+                            const int blk = gi * BPG + b;
+                            uint32_t w[4], x0[4], x1[4];
+                            std::memcpy(w, wp + blk * kSlabBytes, 16);
+                            std::memcpy(x0, xr + blk * 32, 16);
+                            std::memcpy(x1, xr + blk * 32 + 16, 16);
+                            int lo = cp[blk], hi = 0;
                             for (int j = 0; j < 4; ++j) {
                                 lo = dp4a_us(w[j] & 0x0F0F0F0Fu, x0[j], lo);
                                 hi = dp4a_us(w[j] & 0xF0F0F0F0u, x1[j], hi);
@@ -108,9 +109,10 @@ HC_API int pgb_hc_walk(const uint8_t *stream, const float *row_scales, int O, in
                         }
                         if (L.grouped) {
                             float sc;
-                            std::memcpy(&sc, gp - r16 * 16 + L.bpg * kSlabBytes + r16 * 4, 4);
+                            std::memcpy(&sc, sp + gi, 4);
                             acc = acc + sc * (float)dsum;
-                            if (tap && o < O) tap[((size_t)r * O + o) * L.ng + g0 + gi] = dsum;
+                            const int g = chunk * GPC + gi;
+                            if (tap && o < O && g < L.ng_src) tap[((size_t)r * O + o) * L.ng_src + g] = dsum;
                         } else {
                             iacc += dsum;
                         }

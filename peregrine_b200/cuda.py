@@ -489,7 +489,7 @@ class MoeLayer:
             raise CudaError("cuda moe_layer_read_taps failed")
         return gu, dn
 
-    STAGES = ("qrow_x", "route_logits", "route_plan", "gemv_gateup", "qrow_h", "gemv_down", "combine")
+    STAGES = ("qrow_x_unfused", "route", "route_plan_unfused", "gemv_gateup", "qrow_h_unfused", "gemv_down", "unused")
 
     def set_profile(self, on: bool):
         if lib().coli_cuda_moe_layer_set_profile(self.handle, int(on)) != 1:

@@ -23,7 +23,7 @@ def lib():
     return _lib
 
 
-FIELDS = ["O", "K", "grouped", "gs", "bpg", "ng", "nblk", "ntile", "group_bytes", "gpc", "nchunk", "kp",
+FIELDS = ["O", "K", "grouped", "gs", "bpg", "ng_src", "nblk", "ntile", "chunk_bytes", "gpc", "nchunk", "kp",
           "tile_bytes", "total_bytes"]
 
 
@@ -61,7 +61,7 @@ def qrow(x, L):
 def walk(stream, rs, L, xq, cs, sx, nrows, want_tap=False):
     O = L["O"]
     y = np.zeros((nrows, O), np.float32)
-    tap = np.zeros((nrows, O, L["ng"] if L["grouped"] else 1), np.int32) if want_tap else None
+    tap = np.zeros((nrows, O, L["ng_src"] if L["grouped"] else 1), np.int32) if want_tap else None
     xq = np.ascontiguousarray(xq, np.int8)
     cs = np.ascontiguousarray(cs, np.int32)
     sx = np.ascontiguousarray(sx, np.float32)

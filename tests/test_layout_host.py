@@ -28,8 +28,9 @@ def test_repack_roundtrip(O, K, grouped, gs):
     rng = np.random.default_rng(O * 1000 + K)
     q, sc = rand_matrix(rng, O, K, grouped, gs)
     stream, rs, L = hc.repack(q, sc, O, K, grouped, gs)
-    assert L["total_bytes"] == L["ntile"] * L["ng"] * L["group_bytes"]
-    assert L["group_bytes"] * L["gpc"] <= 2176 and L["nchunk"] * L["gpc"] >= L["ng"]
+    assert L["total_bytes"] == L["ntile"] * L["nchunk"] * L["chunk_bytes"]
+    assert L["chunk_bytes"] <= 2560 and L["chunk_bytes"] % 16 == 0 and L["kp"] == L["nchunk"] * 256
+    assert L["gpc"] * L["bpg"] == 8 and (not grouped or L["nchunk"] * L["gpc"] >= L["ng_src"])
     rb = (K + 1) // 2
     for o in rng.integers(0, O, size=min(O, 8)):
         for k in rng.integers(0, K, size=min(K, 40)):
@@ -78,5 +79,7 @@ def test_walk_matches_oracle(O, K, grouped, gs):
 def test_layout_rejects_bad_group_sizes():
     assert hc.layout(16, 64, True, 16) is None
     assert hc.layout(16, 64, True, 48) is None
+    assert hc.layout(16, 64, True, 96) is None
     assert hc.layout(16, 1024, True, 512) is None
-    assert hc.layout(16, 64, True, 32)["gpc"] == 2  # gpc is capped at ng
+    L = hc.layout(2048, 6144, True, 32)  # the benchmark's gate matrix: no padding, container-sized
+    assert L["total_bytes"] == 2048 * 6144 // 2 + 2048 * 6144 // 32 * 4 and L["nchunk"] == 24
