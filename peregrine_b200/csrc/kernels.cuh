@@ -752,71 +752,82 @@ __device__ __forceinline__ void route_plan_body(const float *__restrict__ logits
     for (int i = threadIdx.x; i < plan.n_col; i += blockDim.x) plan.col_done[i] = 0;
     for (int i = threadIdx.x; i < plan.n_amax; i += blockDim.x) plan.amax[i] = 0u;
 
-    // ---- 1. per-token selection, one warp per token
-    float *sig = sig_all + warp * E, *choice = choice_all + warp * E;
-    for (int s = warp; s < M; s += nwarp) {
-        for (int e = lane; e < E; e += 32) {
-            const float sg = sigmoid32(__ldcg(logits + (long long)s * E + e));
-            sig[e] = sg;
-            choice[e] = __fadd_rn(sg, bias[e]);
+    // ---- 1. per-token selection.  Tokens are taken nwarp at a time: all threads evaluate the
+    // sigmoids of the group (the fp64 exponential is the expensive part), then warp w selects
+    // for token g0 + w.  A score is turned into an order-preserving 32-bit key (0 = not
+    // selectable: NaN or -inf, which strict '>' from -inf never picks) so that a round is one
+    // warp-wide integer max plus one integer min for the lowest index among equals.
+    for (int g0 = 0; g0 < M; g0 += nwarp) {
+        const int ng = min(nwarp, M - g0);
+        for (int i = threadIdx.x; i < ng * E; i += blockDim.x) {
+            const int sl = i / E, e = i - sl * E;
+            const float sg = sigmoid32(__ldcg(logits + (long long)(g0 + sl) * E + e));
+            sig_all[sl * E + e] = sg;
+            choice_all[sl * E + e] = __fadd_rn(sg, bias[e]);
         }
-        __syncwarp();
-        int kept = k;
-        // lane kk keeps the kk-th selection of this token (k <= 32)
-        int my_idx = 0;
-        float my_w = 0.0f;
-        for (int kk = 0; kk < k; ++kk) {
-            float bv = -INFINITY;
-            int best = -1;
+        __syncthreads();
+        if (warp < ng) {
+            const int s = g0 + warp;
+            float *sig = sig_all + warp * E;
+            unsigned *key = reinterpret_cast<unsigned *>(choice_all + warp * E);
             for (int e = lane; e < E; e += 32) {
-                const float c = choice[e];
-                if (c > bv) {
-                    bv = c;
-                    best = e;
+                const float c = choice_all[warp * E + e];
+                unsigned u = 0u;
+                if (c > -INFINITY) {  // false for NaN and -inf
+                    u = __float_as_uint(c == 0.0f ? 0.0f : c);
+                    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
                 }
-            }
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, best, o);
-                // a valid candidate always has value > -inf; among equals the lower index wins
-                if (oi >= 0 && (best < 0 || ov > bv || (ov == bv && oi < best))) {
-                    bv = ov;
-                    best = oi;
-                }
-            }
-            if (best < 0) {
-                kept = kk;
-                break;
-            }
-            if (lane == kk) {
-                my_idx = best;
-                my_w = sig[best];
+                key[e] = u;
             }
             __syncwarp();
-            if (lane == 0) choice[best] = -INFINITY;  // never chosen again
-            __syncwarp();
-        }
-        // slots >= kept hold expert 0 with weight 0 (my_idx / my_w initial values)
-        if (norm_topk) {
-            float sm = 0.0f;
-            for (int j = 0; j < k; ++j) sm = __fadd_rn(sm, __shfl_sync(0xffffffffu, my_w, j));
-            sm = __fadd_rn(sm, 1e-20f);
-            my_w = __fdiv_rn(my_w, sm);
-        }
-        my_w = __fmul_rn(my_w, routed_scale);
-        if (lane < k) {
-            plan.idx[s * k + lane] = my_idx;
-            plan.w[s * k + lane] = my_w;
-            if (cached) {
-                idx_c[s * k + lane] = my_idx;
-                w_c[s * k + lane] = my_w;
+            int kept = k;
+            int my_idx = 0;      // lane kk keeps the kk-th selection (k <= 32)
+            float my_w = 0.0f;
+            for (int kk = 0; kk < k; ++kk) {
+                unsigned bu = 0u;
+                int bi = 0x7fffffff;
+                for (int e = lane; e < E; e += 32) {
+                    const unsigned u = key[e];
+                    if (u > bu) {  // ascending e within a lane: the first maximum keeps the lowest index
+                        bu = u;
+                        bi = e;
+                    }
+                }
+                const unsigned top = __reduce_max_sync(0xffffffffu, bu);
+                if (top == 0u) {
+                    kept = kk;
+                    break;
+                }
+                const int best = (int)__reduce_min_sync(0xffffffffu, (unsigned)(bu == top ? bi : 0x7fffffff));
+                if (lane == kk) {
+                    my_idx = best;
+                    my_w = sig[best];
+                }
+                if (lane == 0) key[best] = 0u;  // never chosen again
+                __syncwarp();
+            }
+            // slots >= kept hold expert 0 with weight 0 (the initial values)
+            if (norm_topk) {
+                float sm = 0.0f;
+                for (int j = 0; j < k; ++j) sm = __fadd_rn(sm, __shfl_sync(0xffffffffu, my_w, j));
+                sm = __fadd_rn(sm, 1e-20f);
+                my_w = __fdiv_rn(my_w, sm);
+            }
+            my_w = __fmul_rn(my_w, routed_scale);
+            if (lane < k) {
+                plan.idx[s * k + lane] = my_idx;
+                plan.w[s * k + lane] = my_w;
+                if (cached) {
+                    idx_c[s * k + lane] = my_idx;
+                    w_c[s * k + lane] = my_w;
+                }
+            }
+            if (lane == 0) {
+                plan.keff[s] = kept;
+                if (cached) keff_c[s] = kept;
             }
         }
-        if (lane == 0) {
-            plan.keff[s] = kept;
-            if (cached) keff_c[s] = kept;
-        }
-        __syncwarp();
+        __syncthreads();
     }
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         first_seen[e] = 0x7fffffff;
@@ -838,17 +849,50 @@ __device__ __forceinline__ void route_plan_body(const float *__restrict__ logits
     __syncthreads();
 
     // ---- 3. union position of each routed expert = rank of its first-seen key
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int pos = -1;
-        if (cnt[e] > 0) {
-            pos = 0;
-            const int key = first_seen[e];
-            for (int o = 0; o < E; ++o) pos += (first_seen[o] < key) ? 1 : 0;
-            union_s[pos] = e;
-            plan.union_ids[pos] = e;
-            atomicAdd(s_nunion, 1);
+    if (M * k <= (int)blockDim.x) {
+        // one thread per selection: the selection that first names an expert owns it, and its
+        // rank among such selections (ballot prefix) is the expert's union position
+        for (int e = threadIdx.x; e < E; e += blockDim.x) slot_of[e] = -1;
+        const int q = threadIdx.x;
+        int e_mine = -1;
+        bool owner = false;
+        if (q < M * k) {
+            const int s = q / k, kk = q - s * k;
+            if (kk < ld_keff(s)) {
+                e_mine = ld_idx(q);
+                owner = first_seen[e_mine] == q;
+            }
         }
-        slot_of[e] = pos;
+        const unsigned bal = __ballot_sync(0xffffffffu, owner);
+        unsigned *wcount = mask;  // scratch: owners per warp
+        if (lane == 0) wcount[warp] = __popc(bal);
+        __syncthreads();
+        int before = 0;
+        for (int w2 = 0; w2 < warp; ++w2) before += (int)wcount[w2];
+        if (owner) {
+            const int pos = before + __popc(bal & ((1u << lane) - 1u));
+            union_s[pos] = e_mine;
+            plan.union_ids[pos] = e_mine;
+            slot_of[e_mine] = pos;
+        }
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w2 = 0; w2 < nwarp; ++w2) tot += (int)wcount[w2];
+            *s_nunion = tot;
+        }
+    } else {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            int pos = -1;
+            if (cnt[e] > 0) {
+                pos = 0;
+                const int key = first_seen[e];
+                for (int o = 0; o < E; ++o) pos += (first_seen[o] < key) ? 1 : 0;
+                union_s[pos] = e;
+                plan.union_ids[pos] = e;
+                atomicAdd(s_nunion, 1);
+            }
+            slot_of[e] = pos;
+        }
     }
     __syncthreads();
     const int nunion = *s_nunion;
@@ -950,12 +994,17 @@ __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict
 //     ring by bulk copies issued from a producer warp;
 //   quantiser CTAs (one per token): the int8 copy of x for the gate/up launch;
 //   the chain CTA that finishes last runs route_plan_body.
-constexpr int kRtEPB = 8, kRtMT = 32, kRtSL = 256, kRtMaxStages = 16;
-constexpr int kRtRowFloats = kRtSL + 4;  // 16-byte skew: rows land on distinct banks
-constexpr int kRtThreads = 288;  // 8 chain warps + 1 producer warp
+constexpr int kRtEPB = 8, kRtMT = 32, kRtMaxStages = 16;
+constexpr int kRtThreads = 288;  // 9 warps
 constexpr int kRtRingBytes = 160 * 1024;   // the ring uses as many stages as fit here (at most 16)
 constexpr int kRtBarOffset = kRtRingBytes; // barriers and flags follow the ring
-__host__ __device__ inline int route_stage_bytes(int M) { return (kRtEPB + (M < kRtMT ? M : kRtMT)) * kRtRowFloats * 4; }
+// slice length along D: long slices for a single token (fewer hand-overs on the critical chain)
+__host__ __device__ inline int route_slice(int M) { return M == 1 ? 512 : 256; }
+// floats per operand row inside a stage: 16-byte skew so the 8 router rows land on distinct banks
+__host__ __device__ inline int route_row_floats(int M) { return route_slice(M) + 4; }
+__host__ __device__ inline int route_stage_bytes(int M) {
+    return (kRtEPB + (M < kRtMT ? M : kRtMT)) * route_row_floats(M) * 4;
+}
 __host__ __device__ inline int route_stages(int M) {
     const int n = kRtRingBytes / route_stage_bytes(M);
     return n > kRtMaxStages ? kRtMaxStages : n;
@@ -1027,13 +1076,15 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
     const int e0 = eb * kRtEPB, s0 = sb * kRtMT;
     const int ne = min(kRtEPB, A.E - e0), ns = min(kRtMT, A.M - s0);
     const int kRtStages = route_stages(A.M), kRtStageBytes = route_stage_bytes(A.M);
+    const int kRtSL = route_slice(A.M), kRtRowFloats = route_row_floats(A.M);
     const int xrow0 = kRtEPB;  // token rows follow the 8 router rows inside a stage
     const uint32_t full_u32 = smem_u32(rt_smem + kRtBarOffset);
     const uint32_t empty_u32 = full_u32 + kRtMaxStages * 8;
     if (tid == 0) {
         for (int s = 0; s < kRtStages; ++s) {
             mbar_init(full_u32 + s * 8, 1);
-            mbar_init(empty_u32 + s * 8, 8);
+            mbar_init(empty_u32 + s * 8, A.M == 1 ? 1 : 8);  // decode: only the chain warp releases a stage
+            mbar_init(empty_u32 + kRtMaxStages * 8 + s * 8, 2);  // products ready: warps 1 and 3
         }
         fence_mbar_init();
         fence_proxy_async();
@@ -1041,7 +1092,8 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
     __syncthreads();
     const int nslice = (A.D + kRtSL - 1) / kRtSL;
     bool failed = false;
-    if (warp == 8) {
+    const int producer_warp = (A.M == 1) ? 2 : 8;
+    if (warp == producer_warp) {
         // producer: one bulk copy per operand row and slice (rows 0..ne-1 router, ne.. tokens)
         const int rows = ne + ns;
         for (int i = 0; i < nslice; ++i) {
@@ -1068,6 +1120,99 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
                          (uint32_t)(dlen * 4), full_u32 + st * 8);
             }
         }
+    } else if (A.M == 1) {
+        // Decode: 8 chains in lanes 0-7 of warp 0.  Warps 1 and 3 turn each landed slice into products
+        // in place (p[e][d] = x[d] * w[e][d], the same single rounding the reference's
+        // `acc += xs[d] * wo[d]` applies before its add), so the chain lanes only load and add:
+        // the dependent fp32 add latency is then the only thing on the critical path.  Chain,
+        // product (1, 3) and producer (2) warps sit on four different schedulers; the other warps
+        // wait at the CTA barrier below without issuing, so nothing competes with the chain.
+        const uint32_t prod_u32 = empty_u32 + kRtMaxStages * 8;  // [stage] products ready
+        if (warp >= 4) {
+            // nothing to do until the plan
+        } else if (warp == 1 || warp == 3) {
+            for (int i = 0; i < nslice; ++i) {
+                const int st = i % kRtStages;
+                const bool ok = mbar_wait_bounded(full_u32 + st * 8, (i / kRtStages) & 1u);
+                if (__any_sync(0xffffffffu, !ok)) {
+                    failed = true;
+                    break;
+                }
+                float *stage = reinterpret_cast<float *>(rt_smem + st * kRtStageBytes);
+                const int dlen = min(kRtSL, A.D - i * kRtSL);
+                const int n4 = (dlen + 3) >> 2;  // D is a multiple of 4 on this path
+                // warps 1 and 3 split the slice; four float4 products per lane and step, loads first
+                const int hsel = (warp == 3) ? 1 : 0;
+                const int total4 = ne * n4;
+                for (int q0 = hsel * 32 + lane; q0 < total4; q0 += 4 * 64) {
+                    float4 wq[4], xq4[4];
+                    int off[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int q = q0 + u * 64;
+                        const int e = (q < total4) ? q / n4 : 0;
+                        const int d4 = (q < total4) ? q - e * n4 : 0;
+                        off[u] = (q < total4) ? e * kRtRowFloats + 4 * d4 : -1;
+                        wq[u] = *reinterpret_cast<const float4 *>(stage + (off[u] < 0 ? 0 : off[u]));
+                        xq4[u] = *reinterpret_cast<const float4 *>(stage + xrow0 * kRtRowFloats + 4 * d4);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (off[u] >= 0) {
+                            wq[u].x = __fmul_rn(xq4[u].x, wq[u].x);
+                            wq[u].y = __fmul_rn(xq4[u].y, wq[u].y);
+                            wq[u].z = __fmul_rn(xq4[u].z, wq[u].z);
+                            wq[u].w = __fmul_rn(xq4[u].w, wq[u].w);
+                            *reinterpret_cast<float4 *>(stage + off[u]) = wq[u];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(prod_u32 + st * 8);
+            }
+        } else {
+            const int el = lane & 7;
+            const bool chain = (lane < 8) && (el < ne);
+            float acc = 0.0f;
+            for (int i = 0; i < nslice; ++i) {
+                const int st = i % kRtStages;
+                const bool ok = mbar_wait_bounded(prod_u32 + st * 8, (i / kRtStages) & 1u);
+                if (__any_sync(0xffffffffu, !ok)) {
+                    failed = true;
+                    break;
+                }
+                if (chain) {
+                    const float *pr = reinterpret_cast<const float *>(rt_smem + st * kRtStageBytes) + el * kRtRowFloats;
+                    const int dlen = min(kRtSL, A.D - i * kRtSL);
+                    if (dlen == kRtSL) {
+                        float4 pv[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) pv[j] = *reinterpret_cast<const float4 *>(pr + 4 * j);
+#pragma unroll 1
+                        for (int d = 0; d < kRtSL; d += 16) {
+                            float4 pn[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                // the load past the last step reads the head of the next row of the
+                                // stage (router rows are always followed by the token row) and is unused
+                                pn[j] = *reinterpret_cast<const float4 *>(pr + d + 16 + 4 * j);
+                                acc = __fadd_rn(acc, pv[j].x);
+                                acc = __fadd_rn(acc, pv[j].y);
+                                acc = __fadd_rn(acc, pv[j].z);
+                                acc = __fadd_rn(acc, pv[j].w);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) pv[j] = pn[j];
+                        }
+                    } else {
+                        for (int d = 0; d < dlen; ++d) acc = __fadd_rn(acc, pr[d]);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_u32 + st * 8);
+            }
+            if (chain && !failed) A.logits[(long long)s0 * A.E + e0 + el] = acc;
+        }
     } else {
         const int el = tid & 7, sl = tid >> 3;
         const bool chain = (el < ne) && (sl < ns);
@@ -1085,14 +1230,46 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
                     reinterpret_cast<const float *>(rt_smem + st * kRtStageBytes) + (xrow0 + sl) * kRtRowFloats;
                 const int dlen = min(kRtSL, A.D - i * kRtSL);
                 if (dlen == kRtSL) {
-#pragma unroll 8
-                    for (int d = 0; d < kRtSL; d += 4) {
-                        const float4 w4 = *reinterpret_cast<const float4 *>(wr + d);
-                        const float4 x4 = *reinterpret_cast<const float4 *>(xr + d);
-                        acc = __fadd_rn(acc, __fmul_rn(x4.x, w4.x));
-                        acc = __fadd_rn(acc, __fmul_rn(x4.y, w4.y));
-                        acc = __fadd_rn(acc, __fmul_rn(x4.z, w4.z));
-                        acc = __fadd_rn(acc, __fmul_rn(x4.w, w4.w));
+                    // three-stage software pipeline written out in source order: the adds of step i are
+                    // interleaved with the multiplies of step i+1 and the loads of step i+2, so the
+                    // independent work fills the issue slots the dependent adds leave free
+                    float4 wv[4], xv[4];
+                    float p[16];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        wv[j] = *reinterpret_cast<const float4 *>(wr + 4 * j);
+                        xv[j] = *reinterpret_cast<const float4 *>(xr + 4 * j);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        p[4 * j + 0] = __fmul_rn(xv[j].x, wv[j].x);
+                        p[4 * j + 1] = __fmul_rn(xv[j].y, wv[j].y);
+                        p[4 * j + 2] = __fmul_rn(xv[j].z, wv[j].z);
+                        p[4 * j + 3] = __fmul_rn(xv[j].w, wv[j].w);
+                        wv[j] = *reinterpret_cast<const float4 *>(wr + 16 + 4 * j);
+                        xv[j] = *reinterpret_cast<const float4 *>(xr + 16 + 4 * j);
+                    }
+#pragma unroll 1
+                    for (int d = 0; d < kRtSL; d += 16) {
+                        float pn[16];
+                        // loads two steps ahead stay inside the padded row of this stage or read the
+                        // next row of the stage; values past the slice are never added
+                        const int dl = min(d + 32, kRtSL - 16);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc = __fadd_rn(acc, p[4 * j + 0]);
+                            pn[4 * j + 0] = __fmul_rn(xv[j].x, wv[j].x);
+                            acc = __fadd_rn(acc, p[4 * j + 1]);
+                            pn[4 * j + 1] = __fmul_rn(xv[j].y, wv[j].y);
+                            acc = __fadd_rn(acc, p[4 * j + 2]);
+                            pn[4 * j + 2] = __fmul_rn(xv[j].z, wv[j].z);
+                            acc = __fadd_rn(acc, p[4 * j + 3]);
+                            pn[4 * j + 3] = __fmul_rn(xv[j].w, wv[j].w);
+                            wv[j] = *reinterpret_cast<const float4 *>(wr + dl + 4 * j);
+                            xv[j] = *reinterpret_cast<const float4 *>(xr + dl + 4 * j);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) p[j] = pn[j];
                     }
                 } else {
                     for (int d = 0; d < dlen; ++d) acc = __fadd_rn(acc, __fmul_rn(xr[d], wr[d]));
@@ -1107,7 +1284,7 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
     // ---------------- the last chain CTA to finish plans the layer
     __threadfence();
     __syncthreads();
-    int *s_last = reinterpret_cast<int *>(rt_smem + kRtBarOffset + 2 * kRtMaxStages * 8);
+    int *s_last = reinterpret_cast<int *>(rt_smem + kRtBarOffset + 3 * kRtMaxStages * 8);
     if (tid == 0) {
         const unsigned old = atomicAdd(A.done_counter, 1u);
         *s_last = (old == (unsigned)A.n_chain_ctas - 1u);
