@@ -11,6 +11,7 @@
 
 #include "../../include/peregrine_b200.h"
 #include "kernels.cuh"
+#include "kernels_mma.cuh"
 #include "w4_host.h"
 
 using namespace pgb;
@@ -422,15 +423,58 @@ static int gemv_launch_r(Ctx *c, const GemvParams &P, bool grouped, int bpg, int
     return fail("w4a8 gemv: unsupported group size");
 }
 
-// True when the launch's activation rows fit in shared memory beside the rings.
+// ---- small-batch (tensor-core) variant: 3 or more rows in some slot
+static size_t mma_xs_bytes(int n_xrows, int kp, int nblk) {
+    return (((size_t)n_xrows * (kp + kMmaRowPad) + 15) & ~(size_t)15) + (size_t)n_xrows * nblk * 4 +
+           (size_t)n_xrows * 4 + 16;
+}
+
+template <int NT, bool GROUPED, int BPG, int XS, bool TAP>
+static int mma_launch_t(Ctx *c, const GemvParams &P, size_t smem) {
+    auto kfn = gemv_w4a8_mma_kernel<NT, GROUPED, BPG, XS, TAP>;
+    static std::atomic<uint32_t> configured{0};
+    const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
+    if (!(configured.load() & bit)) {
+        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->smem_optin),
+                     "mma gemv shared-memory opt-in"))
+            return 0;
+        configured.fetch_or(bit);
+    }
+    return launch(kfn, dim3(c->sms), dim3(kMmaThreads), smem, c->stream, "w4a8 mma gemv launch", P);
+}
+
+template <int NT, bool GROUPED, int BPG>
+static int mma_launch_x(Ctx *c, const GemvParams &P, bool xs, size_t smem) {
+    if (P.tap) return xs ? mma_launch_t<NT, GROUPED, BPG, 1, true>(c, P, smem)
+                         : mma_launch_t<NT, GROUPED, BPG, 0, true>(c, P, smem);
+    return xs ? mma_launch_t<NT, GROUPED, BPG, 1, false>(c, P, smem) : mma_launch_t<NT, GROUPED, BPG, 0, false>(c, P, smem);
+}
+
+template <int NT>
+static int mma_launch_r(Ctx *c, const GemvParams &P, bool grouped, int bpg, bool xs, size_t smem) {
+    if (!grouped) return mma_launch_x<NT, false, 1>(c, P, xs, smem);
+    switch (bpg) {
+        case 1: return mma_launch_x<NT, true, 1>(c, P, xs, smem);
+        case 2: return mma_launch_x<NT, true, 2>(c, P, xs, smem);
+        case 4: return mma_launch_x<NT, true, 4>(c, P, xs, smem);
+        case 8: return mma_launch_x<NT, true, 8>(c, P, xs, smem);
+    }
+    return fail("w4a8 mma gemv: unsupported group size");
+}
+
+// True when the launch's activation rows fit in shared memory beside the rings of the dp4a kernel.
 static bool gemv_rows_fit(Ctx *c, int n_xrows, const W4Layout &L) {
     return (size_t)kRingBytes + kGemvBarBytes + gemv_xs_bytes(n_xrows, L.kp, L.nblk) + 1024 <= c->smem_optin;
 }
+// True when a down launch with these bounds will quantise its fp32 rows itself.
+static bool gemv_can_quant_stage(Ctx *c, int n_xrows, const W4Layout &L, int max_rows) {
+    return max_rows <= 2 && gemv_rows_fit(c, n_xrows, L);
+}
 
-// Fills the layout-dependent fields and launches.  `max_rows` bounds the rows of any slot.
-// `want_quant_stage`: the caller filled x_f32 / amax_bits and prefers the kernel to quantise
-// the rows itself; honoured only when the rows fit in shared memory (the return value of
-// gemv_rows_fit tells the caller beforehand).
+// Fills the layout-dependent fields and launches.  `max_rows` bounds the rows of any slot:
+// up to 2 rows run the dp4a kernel, more run the tensor-core kernel.
+// `want_quant_stage`: the caller filled x_f32 / amax_bits and wants the kernel to quantise the
+// rows itself; only valid when gemv_can_quant_stage() said so.
 static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_rows, bool want_quant_stage = false) {
     P.mode = mode;
     P.nchunk = L.nchunk;
@@ -444,16 +488,23 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
     P.xq_stride = L.kp;
     P.cs_stride = L.nblk;
     P.err = c->err_dev;
+    const bool grouped = L.grouped != 0;
+    if (max_rows > 2) {
+        if (want_quant_stage) return fail("w4a8 gemv: quantising stage is not available beyond 2 rows per expert");
+        const size_t base = (size_t)kMmaRingBytes + kMmaBarBytes;
+        const size_t need = mma_xs_bytes(P.n_xrows, L.kp, L.nblk);
+        const bool xs = base + need + 1024 <= c->smem_optin;
+        const size_t smem = base + (xs ? need : 0);
+        if (max_rows <= 8) return mma_launch_r<1>(c, P, grouped, L.bpg, xs, smem);
+        return mma_launch_r<2>(c, P, grouped, L.bpg, xs, smem);
+    }
     const size_t base = (size_t)kRingBytes + kGemvBarBytes;
     const bool fit = gemv_rows_fit(c, P.n_xrows, L);
     const int xs = fit ? (want_quant_stage ? 2 : 1) : 0;
     if (want_quant_stage && !fit) return fail("w4a8 gemv: quantising stage requested but rows do not fit");
     const size_t smem = base + (fit ? gemv_xs_bytes(P.n_xrows, L.kp, L.nblk) : 0);
-    const bool grouped = L.grouped != 0;
     if (max_rows <= 1) return gemv_launch_r<1>(c, P, grouped, L.bpg, xs, smem);
-    if (max_rows <= 2) return gemv_launch_r<2>(c, P, grouped, L.bpg, xs, smem);
-    if (max_rows <= 4) return gemv_launch_r<4>(c, P, grouped, L.bpg, xs, smem);
-    return gemv_launch_r<8>(c, P, grouped, L.bpg, xs, smem);
+    return gemv_launch_r<2>(c, P, grouped, L.bpg, xs, smem);
 }
 
 static int qrow_run(Ctx *c, const float *x, long long ldx, int K, const W4Layout &L, int8_t *xq, float *sx, int *cs,

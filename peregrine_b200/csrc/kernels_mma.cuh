@@ -1,0 +1,336 @@
+// Small-batch variant of the int4 x int8 expert matmul: 3 to ~32 activation rows
+// per expert.  Same tile stream, ring, cursor and epilogues as gemv_w4a8_kernel
+// (kernels.cuh); the integer block dots are formed by the warp-level int8 MMA
+// (m16n8k32, u8 x s8 -> s32) instead of dp4a, so one instruction covers 16 weight
+// rows x 8 activation rows x 32 elements.  The fp32 side is unchanged: per (row,
+// activation row) one lane folds the group dots in ascending group order, one
+// multiply and one add at a time (crates/peregrine-kernels/src/idot.rs:98-110,
+// matmul.rs:75-106).
+//
+// Fragment fit: lane (g = lane/4, t = lane%4) of an m16n8k32 MMA holds, of the A
+// operand, elements [4t, 4t+4) and [16+4t, 16+4t+4) of rows g and g+8.  Word t of
+// a row's 16-byte segment in the tile stream is exactly elem[4t..4t+3] in its low
+// nibbles and elem[16+4t..] in its high nibbles, so two 32-bit loads and four
+// mask/shift operations build the whole A fragment.  Stored nibbles are v+8; the
+// accumulator therefore starts from -8*sum(q) of the activation block (the same
+// correction the dp4a kernel uses).
+#pragma once
+#include "kernels.cuh"
+
+namespace pgb {
+
+constexpr int kMmaWarps = 8;
+constexpr int kMmaStages = 3;
+constexpr int kMmaThreads = kMmaWarps * 32;
+constexpr int kMmaRingBytes = kMmaWarps * kMmaStages * kStageBytes;
+constexpr int kMmaBarBytes = ((kMmaWarps * kMmaStages * 8 + 127) / 128) * 128;
+constexpr int kMmaRowPad = 16;  // bytes of skew per staged activation row (bank spread for the B loads)
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// NT = 8-row activation groups per pass (rows per pass = 8 * NT).
+// XS = 0: activation rows read from global memory; 1: int8 rows copied to shared memory.
+template <int NT, bool GROUPED, int BPG, int XS, bool TAP>
+__global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const GemvParams P) {
+    constexpr int RMAX = 8 * NT;
+    constexpr int GPC = kChunkBlocks / BPG;
+    constexpr int CHUNK_BYTES = kChunkSlabBytes + (GROUPED ? GPC * 64 : 0);
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    uint8_t *ring = smem + warp * (kMmaStages * kStageBytes);
+    const uint32_t ring_u32 = smem_u32(ring);
+    const uint32_t bar_u32 = smem_u32(smem + kMmaRingBytes) + warp * (kMmaStages * 8);
+    int8_t *xs = reinterpret_cast<int8_t *>(smem + kMmaRingBytes + kMmaBarBytes);
+    const int xs_stride = P.xq_stride + kMmaRowPad;
+    const int xs_bytes = (P.n_xrows * xs_stride + 15) & ~15;
+    int *cs_s = reinterpret_cast<int *>(xs + xs_bytes);
+    float *sx_s = reinterpret_cast<float *>(cs_s + P.n_xrows * P.cs_stride);
+
+    if (lane == 0) {
+        for (int s = 0; s < kMmaStages; ++s) mbar_init(bar_u32 + s * 8, 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncwarp();
+
+    const int n_slots = *P.n_slots;
+    const int total = n_slots * P.warp_tiles;
+    const int stride = gridDim.x * kMmaWarps;
+
+    TileCursor fc, cc;
+    fc.i = blockIdx.x + gridDim.x * warp;
+    fc.pass = 0;
+    fc.chunk = 0;
+    cursor_seek<RMAX>(fc, P, total, stride);
+    cc = fc;
+    uint32_t fq = 0, cq = 0;
+
+    auto issue = [&](const TileCursor &c, uint32_t q) {
+        const uint32_t stage = q % kMmaStages;
+        const uint32_t bar = bar_u32 + stage * 8;
+        const uint32_t dst = ring_u32 + stage * kStageBytes;
+        const size_t off = (size_t)c.chunk * CHUNK_BYTES;
+        mbar_expect_tx(bar, c.b ? 2 * CHUNK_BYTES : CHUNK_BYTES);
+        bulk_g2s(dst, c.a + off, CHUNK_BYTES, bar);
+        if (c.b) bulk_g2s(dst + kChunkMaxBytes, c.b + off, CHUNK_BYTES, bar);
+    };
+    while (fc.i < total && fq < cq + kMmaStages) {
+        if (lane == 0) issue(fc, fq);
+        cursor_next<RMAX>(fc, P, total, stride);
+        ++fq;
+    }
+
+    if (XS == 1) {
+        // row by row: the shared-memory rows carry a 16-byte skew
+        const int v_per_row = P.xq_stride >> 4;
+        for (int i = threadIdx.x; i < P.n_xrows * v_per_row; i += blockDim.x) {
+            const int row = i / v_per_row, v = i - row * v_per_row;
+            *reinterpret_cast<uint4 *>(xs + (size_t)row * xs_stride + 16 * v) =
+                *reinterpret_cast<const uint4 *>(P.xq + (size_t)row * P.xq_stride + 16 * v);
+        }
+        const int ncs = P.n_xrows * P.cs_stride;
+        for (int i = threadIdx.x; i < ncs; i += blockDim.x) cs_s[i] = P.csum[i];
+        for (int i = threadIdx.x; i < P.n_xrows; i += blockDim.x) sx_s[i] = P.sx[i];
+        __syncthreads();
+    }
+    const int8_t *xbase = XS ? xs : P.xq;
+    const int xstride = XS ? xs_stride : P.xq_stride;
+    const int *csbase = XS ? cs_s : P.csum;
+    const float *sxbase = XS ? sx_s : P.sx;
+
+    // accumulators: [half][n-tile][fragment slot]; slot i: row g + 8*(i>>1), column 2t + (i&1)
+    float acc[2][NT][4];
+    int iacc[2][NT][4];
+    int csacc[NT][2];   // per-row format: running -8*sum over the whole K, columns 2t, 2t+1
+    int arow_b[NT];     // activation row feeding this lane's B fragment (column g of n-tile nt)
+    int arow_c[NT][2];  // activation rows of this lane's accumulator columns 2t, 2t+1
+    bool failed = false;
+
+    while (cc.i < total) {
+        if (fc.i < total && fq < cq + kMmaStages) {
+            if (lane == 0) {
+                fence_proxy_async();
+                issue(fc, fq);
+            }
+            cursor_next<RMAX>(fc, P, total, stride);
+            ++fq;
+        }
+        const uint32_t stage = cq % kMmaStages;
+        const uint32_t parity = (cq / kMmaStages) & 1u;
+        {
+            const bool ok = mbar_wait_bounded(bar_u32 + stage * 8, parity);
+            if (__any_sync(0xffffffffu, !ok)) {
+                if (lane == 0) atomicExch(P.err, kErrBarrierTimeout);
+                failed = true;
+                break;
+            }
+        }
+        if (cc.chunk == 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        acc[h][nt][i] = 0.0f;
+                        iacc[h][nt][i] = 0;
+                    }
+                csacc[nt][0] = csacc[nt][1] = 0;
+                const int rb = min(cc.pass * RMAX + 8 * nt + g, cc.nrows - 1);
+                arow_b[nt] = P.rowmap ? P.rowmap[cc.row0 + rb] : cc.row0 + rb;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int rc = min(cc.pass * RMAX + 8 * nt + 2 * t + j, cc.nrows - 1);
+                    arow_c[nt][j] = P.rowmap ? P.rowmap[cc.row0 + rc] : cc.row0 + rc;
+                }
+            }
+        }
+        const uint8_t *st = ring + stage * kStageBytes;
+#pragma unroll
+        for (int gi = 0; gi < GPC; ++gi) {
+            int c[2][NT][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) c[h][nt][i] = 0;
+            int csg[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) csg[nt][0] = csg[nt][1] = 0;
+#pragma unroll
+            for (int b = 0; b < BPG; ++b) {
+                const int blk = gi * BPG + b;
+                uint32_t b0[NT], b1[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int8_t *xr = xbase + (size_t)arow_b[nt] * xstride + cc.chunk * kChunkElems + blk * 32 + 4 * t;
+                    if (XS) {
+                        b0[nt] = *reinterpret_cast<const uint32_t *>(xr);
+                        b1[nt] = *reinterpret_cast<const uint32_t *>(xr + 16);
+                    } else {
+                        b0[nt] = __ldg(reinterpret_cast<const uint32_t *>(xr));
+                        b1[nt] = __ldg(reinterpret_cast<const uint32_t *>(xr + 16));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int *cp = csbase + (size_t)arow_c[nt][j] * P.cs_stride + cc.chunk * kChunkBlocks + blk;
+                        csg[nt][j] += XS ? *cp : __ldg(cp);
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint8_t *wp = st + h * kChunkMaxBytes + blk * kSlabBytes + t * 4;
+                    const uint32_t w0 = *reinterpret_cast<const uint32_t *>(wp + g * 16);
+                    const uint32_t w1 = *reinterpret_cast<const uint32_t *>(wp + (g + 8) * 16);
+                    const uint32_t a0 = w0 & 0x0F0F0F0Fu, a2 = (w0 >> 4) & 0x0F0F0F0Fu;
+                    const uint32_t a1 = w1 & 0x0F0F0F0Fu, a3 = (w1 >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) mma_u8s8(c[h][nt], a0, a1, a2, a3, b0[nt], b1[nt]);
+                }
+            }
+            if (GROUPED) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float *sp = reinterpret_cast<const float *>(st + h * kChunkMaxBytes + kChunkSlabBytes);
+                    const float sc_lo = sp[g * GPC + gi], sc_hi = sp[(g + 8) * GPC + gi];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int d = c[h][nt][i] + csg[nt][i & 1];
+                            acc[h][nt][i] = __fadd_rn(acc[h][nt][i], __fmul_rn(i < 2 ? sc_lo : sc_hi, (float)d));
+                            if (TAP) {
+                                const int ridx = cc.pass * RMAX + 8 * nt + 2 * t + (i & 1);
+                                const int r = g + 8 * (i >> 1);
+                                const int o = (P.mode == 0) ? cc.tile * 16 + r : (2 * cc.tile + h) * 16 + r;
+                                const int gg = cc.chunk * GPC + gi;
+                                if (P.tap != nullptr && ridx < cc.nrows && o < P.O && gg < P.ng_tap && (h == 0 || cc.b)) {
+                                    const long long base = (P.mode == 0)
+                                                               ? ((long long)(cc.row0 + ridx) * 2 + h) * P.O + o
+                                                               : (long long)(cc.row0 + ridx) * P.O + o;
+                                    P.tap[base * P.ng_tap + gg] = d;
+                                }
+                            }
+                        }
+                }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    csacc[nt][0] += csg[nt][0];
+                    csacc[nt][1] += csg[nt][1];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) iacc[h][nt][i] += c[h][nt][i];
+                }
+            }
+        }
+        __syncwarp();
+        if (cc.chunk == P.nchunk - 1) {
+            // value of accumulator slot (h, nt, i) after the activation scale
+            auto value = [&](int h, int nt, int i, int o) -> float {
+                const float sxa = sxbase[arow_c[nt][i & 1]];
+                if (GROUPED) return __fmul_rn(acc[h][nt][i], sxa);
+                const float *rsp = (P.mode == 0 && h) ? cc.b_rs : cc.a_rs;
+                const float rs = (o < P.ntile * 16) ? rsp[o] : 0.0f;
+                const int d = iacc[h][nt][i] + csacc[nt][i & 1];
+                if (TAP && P.tap != nullptr && o < P.O && (h == 0 || cc.b)) {
+                    const int ridx = cc.pass * RMAX + 8 * nt + 2 * t + (i & 1);
+                    if (ridx < cc.nrows) {
+                        const long long base = (P.mode == 0) ? ((long long)(cc.row0 + ridx) * 2 + h) * P.O + o
+                                                             : (long long)(cc.row0 + ridx) * P.O + o;
+                        P.tap[base] = d;
+                    }
+                }
+                return __fmul_rn(__fmul_rn((float)d, rs), sxa);
+            };
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                float amax2[2] = {0.0f, 0.0f};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int ridx = cc.pass * RMAX + 8 * nt + 2 * t + (i & 1);
+                    const bool valid = ridx < cc.nrows;
+                    const int r = g + 8 * (i >> 1);
+                    if (P.mode == 0) {
+                        const int o = cc.tile * 16 + r;
+                        const float vg = value(0, nt, i, o), vu = value(1, nt, i, o);
+                        if (valid && o < P.O) {
+                            const float hval = __fmul_rn(silu32(vg), vu);
+                            P.out[(long long)(cc.row0 + ridx) * P.out_stride + o] = hval;
+                            const float a = fabsf(hval);
+                            if (a == a) amax2[i & 1] = fmaxf(amax2[i & 1], a);  // NaN never becomes the maximum
+                        }
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int o = (2 * cc.tile + h) * 16 + r;
+                            const float v = value(h, nt, i, o);
+                            if (valid && o < P.O && (h == 0 || cc.b))
+                                P.out[(long long)(cc.row0 + ridx) * P.out_stride + o] = v;
+                        }
+                    }
+                }
+                if (P.mode == 0 && P.amax_out != nullptr) {
+                    // row maxima of |h|: reduce over the 8 lanes that share this lane's two columns
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        float a = amax2[j];
+                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 8));
+                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+                        const int ridx = cc.pass * RMAX + 8 * nt + 2 * t + j;
+                        if (g == 0 && ridx < cc.nrows && a > 0.0f)
+                            atomicMax(P.amax_out + cc.row0 + ridx, __float_as_uint(a));
+                    }
+                }
+            }
+            if (P.mode == 1 && P.comb.col_done != nullptr && cc.pass == cc.npass - 1) {
+                // ordered combine by the warp that completes an output column tile (see gemv_w4a8_kernel)
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) last = (atomicAdd(P.comb.col_done + cc.tile, 1) == n_slots - 1);
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    const int col = cc.tile * 32 + lane;
+                    const int sp0 = *P.comb.shared_pair0;
+                    if (col < P.O) {
+                        for (int s = 0; s < P.comb.M; ++s) {
+                            const int ke = P.comb.keff[s];
+                            float a = 0.0f;
+                            for (int j = 0; j < ke; ++j) {
+                                const int p = P.comb.comb_pair[s * P.comb.k + j];
+                                const float wgt = P.comb.comb_w[s * P.comb.k + j];
+                                a = __fadd_rn(a, __fmul_rn(wgt, __ldcg(P.out + (long long)p * P.out_stride + col)));
+                            }
+                            if (sp0 >= 0) a = __fadd_rn(a, __ldcg(P.out + (long long)(sp0 + s) * P.out_stride + col));
+                            P.comb.out[(long long)s * P.comb.ldo + col] = a;
+                        }
+                    }
+                }
+            }
+        }
+        cursor_next<RMAX>(cc, P, total, stride);
+        ++cq;
+    }
+    if (failed) {
+        for (uint32_t q = cq; q < fq; ++q) {
+            const uint32_t stage = q % kMmaStages, parity = (q / kMmaStages) & 1u;
+            const long long t0 = clock64();
+            while (!mbar_try_wait(bar_u32 + stage * 8, parity))
+                if (clock64() - t0 > 200000000LL) break;
+        }
+    }
+}
+
+}  // namespace pgb
