@@ -327,6 +327,26 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         "hbm_frac_of_8000_whole_step": total_b / (total_ms / args.steps * 1e-3) / 1e9 / 8000.0,
         "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
     }
+    if world == 1 and m == 1:
+        # the same layer at the batch of the expert-parallel runs, on this one GPU: the base the
+        # N > 1 lines of this bench (strong scaling at batch 32) compare with
+        xb_host = synth_tokens(7, 8 * EP_BATCH, c["hidden"]).reshape(8, EP_BATCH, c["hidden"])
+        with torch.cuda.stream(stream):
+            xb = torch.from_numpy(xb_host).cuda(dev)
+            ob = torch.empty((EP_BATCH, c["hidden"]), dtype=torch.float32, device=dev)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(40)]
+        for i in range(45):
+            with torch.cuda.stream(stream):
+                flush_l2()
+                if i >= 5:
+                    evs[i - 5][0].record(stream)
+                ml.forward_dev(ob.data_ptr(), xb[i % 8].data_ptr(), EP_BATCH)
+                if i >= 5:
+                    evs[i - 5][1].record(stream)
+        stream.synchronize()
+        ms32 = float(np.mean([a.elapsed_time(b) for a, b in evs]))
+        line["ep_batch32"] = {"value": EP_BATCH / (ms32 * 1e-3), "unit": UNIT, "ms_per_step": ms32, "m": EP_BATCH,
+                              "steps": 40}
     if rank == 0 and world == 1 and not args.no_cpu:
         import oracle as po
 
@@ -343,6 +363,135 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     if dist:
         dist.barrier()
         dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+EP_BATCH = 32  # configs[4]: decode batch of the expert-parallel runs
+
+
+def run_ep(args, rank: int, local_rank: int, world: int):
+    """N > 1: one MoE decode layer of configs[4], batch 32, routed experts split over the ranks
+    (256/N per GPU), router and shared expert replicated, NCCL all-gather / sum-reduction around
+    the expert kernels.  Strong scaling: the batch is fixed."""
+    import torch
+    import torch.distributed as dist
+
+    from peregrine_b200 import cuda
+    from peregrine_b200.ep import EpLayerRunner, owned_range
+    from peregrine_b200.resident import upload_expert
+    from peregrine_b200.synth import synth_expert, synth_tokens, zipf_bias
+
+    c = CFG
+    dev = local_rank
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", dev))
+    if cuda.init([dev]) < 1:
+        raise RuntimeError("bench: the CUDA backend could not initialise its device (no CPU fallback exists)")
+    m_total = args.m if args.m > 1 else EP_BATCH
+    m_local = m_total // world
+    rng = np.random.default_rng(1234)  # router identical on every rank
+    router_w = (rng.standard_normal((c["n_experts"], c["hidden"])).astype(np.float32) * np.float32(0.02))
+    bias = zipf_bias(rng, c["n_experts"])
+    ml = cuda.MoeLayer(dev, c["hidden"], c["inter"], c["n_experts"], c["k"], c["norm_topk"], c["routed_scale"],
+                       router_w, bias)
+    ml.set_ep(rank, world)
+    for e in owned_range(c["n_experts"], rank, world):
+        ml.set_expert(e, upload_expert(dev, synth_expert(np.random.default_rng(5000 + e), c["hidden"], c["inter"],
+                                                         c["gs"]), c["hidden"], c["inter"]))
+    ml.set_shared(upload_expert(dev, synth_expert(np.random.default_rng(4999), c["hidden"], c["inter"], c["gs"]),
+                                c["hidden"], c["inter"]))
+    run = EpLayerRunner(ml, dev, rank, world, m_total)
+    stream = run.stream
+    xs_host = synth_tokens(99, N_TOKENS * m_total, c["hidden"]).reshape(N_TOKENS, m_total, c["hidden"])
+    xs_host = np.ascontiguousarray(xs_host[:, rank * m_local:(rank + 1) * m_local, :])
+    with torch.cuda.stream(stream):
+        xs = torch.from_numpy(xs_host).cuda(dev)
+        flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
+        drain = torch.zeros(FLUSH_BYTES // 4, dtype=torch.float32, device=dev)
+        x_pin = torch.from_numpy(xs_host).pin_memory()
+        x_dev = torch.empty((m_local, c["hidden"]), dtype=torch.float32, device=dev)
+    stream.synchronize()
+
+    def step(i, ev=None):
+        with torch.cuda.stream(stream):
+            flush.zero_()
+            drain.sum()
+            if ev:
+                ev[0].record(stream)
+            run.forward(xs[i % N_TOKENS])
+            if ev:
+                ev[1].record(stream)
+
+    for i in range(args.warmup):
+        step(i)
+    stream.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    n0 = cuda.kernel_launches()
+    with ClockSampler(dev) as clocks:
+        for i in range(args.steps):
+            step(i, events[i])
+        stream.synchronize()
+    torch.cuda.synchronize()
+    dist.barrier()
+    launches = cuda.kernel_launches() - n0
+    total_ms = float(sum(a.elapsed_time(b) for a, b in events))
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    if cuda.last_device_error(dev) != 0:
+        raise RuntimeError("bench: a kernel reported a device-side error")
+    value = m_total * args.steps / (total_ms * 1e-3)
+    n_union = len(ml.last_routing(m_total)[3])
+    # end to end: pinned host tokens in, home-token outputs back to the host, every step
+    e2e_steps = min(args.steps, 200)
+    e2e_t = 0.0
+    for i in range(e2e_steps):
+        with torch.cuda.stream(stream):
+            flush.zero_()
+            drain.sum()
+        stream.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        with torch.cuda.stream(stream):
+            x_dev.copy_(x_pin[i % N_TOKENS], non_blocking=True)
+            out = run.forward(x_dev)
+            host = out.to("cpu", non_blocking=False)
+        e2e_t += time.perf_counter() - t0
+        del host
+    t = torch.tensor([e2e_t], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_t = float(t.item())
+    total_b, gu_b, dn_b = algorithmic_bytes(n_union, m_total)
+    peak, peak_kind = measured_peaks()
+    step_s = total_ms / args.steps * 1e-3
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int4 x int8 -> int32 -> f32", "data": "synthetic",
+        "config": {"workload": f"configs[4] MoE layer, expert-parallel: decode batch {m_total} fixed, hidden 6144, "
+                               f"256 routed experts top-8 split {c['n_experts'] // world} per GPU + replicated "
+                               "shared expert, moe_inter 2048, int4 group-32, Zipf(1.1) selection bias",
+                   "m": m_total, "parallelism": f"ep{world}: all-gather of tokens, sum-reduction of pair rows (NCCL)",
+                   "l2": "flushed before every step, untimed: 256 MiB written, then 256 MiB read",
+                   "union": n_union,
+                   "note": "the N=1 line of this bench is configs[1] (M=1); its ep_batch32 entry is the "
+                           "single-GPU time of this same batch-32 layer"},
+        "roofline": {"bound": "hbm", "kernel": "whole layer step (all ranks)", "achieved": total_b / step_s / 1e9,
+                     "peak": peak * world, "peak_kind": f"{peak_kind} copy bandwidth x {world} GPUs", "unit": "GB/s",
+                     "frac": total_b / step_s / 1e9 / (peak * world), "traffic": None,
+                     "algorithmic_bytes": total_b},
+        "e2e": {"value": m_total * e2e_steps / e2e_t, "unit": UNIT, "h2d_bytes_per_step": m_local * c["hidden"] * 4,
+                "d2h_bytes_per_step": m_local * c["hidden"] * 4, "steps": e2e_steps,
+                "call": "EpLayerRunner.forward on this rank's home tokens (pinned host in, host out)"},
+        "gpu_launches": int(launches), "clocks": clocks.summary(),
+    }
+    ml.free()
+    cuda.shutdown()
+    dist.barrier()
+    dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line), flush=True)
 
@@ -365,6 +514,8 @@ def main():
     CFG["n_experts"] = args.experts
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif world > 1:
+        run_ep(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)
 

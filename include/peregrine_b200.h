@@ -202,6 +202,20 @@ int coli_cuda_moe_layer_last_pairs(ColiCudaMoeLayer *layer, int *n_pairs, int *p
 int coli_cuda_moe_layer_read_taps(ColiCudaMoeLayer *layer, int32_t *gateup_taps, size_t gateup_count,
                                   int32_t *down_taps, size_t down_count);
 
+/* Expert parallelism over the GPUs of one node (the reference has none: crates/peregrine-model/src/gpu.rs:1454-1457
+ * hard-codes one device; docs/scale-out-design.md:34-72 sketches an owner map per (layer, expert) and requires
+ * cross-device partial sums in fixed order).  Rank r of `world` owns the routed experts
+ * [r*ceil(E/world), (r+1)*ceil(E/world)) and only those need to be attached; router and shared expert are
+ * replicated.  Every rank runs the partial forward on the WHOLE batch x_all[M, D] (all ranks route
+ * identically): it writes the pair rows [M*(k+1), D] of its own experts, and of the shared expert for its home
+ * tokens [r*ceil(M/world), ...), and zeros elsewhere.  The caller sums the buffers of all ranks (each row has
+ * one non-zero contributor, so the sum is exact in any order) and then combines its home tokens in
+ * batch-union order: out[i, :] is token first_token + i. */
+int coli_cuda_moe_layer_set_ep(ColiCudaMoeLayer *layer, int rank, int world);
+int coli_cuda_moe_layer_ep_partial_dev(ColiCudaMoeLayer *layer, float *y_pairs_dev, const float *x_all_dev, int M);
+int coli_cuda_moe_layer_ep_combine_dev(ColiCudaMoeLayer *layer, float *out_dev, const float *y_pairs_dev, int M,
+                                       int first_token, int n_tokens);
+
 /* Profile mode (in the spirit of COLI_CUDA_PROFILE, cuda/backend_cuda.cu:1068,1174-1207):
  * each forward brackets its seven launches with events, waits for the stream and
  * accumulates per-stage device milliseconds: quantise x, router logits, routing plan,

@@ -700,6 +700,9 @@ struct RoutePlan {
     int n_col;
     unsigned *amax;     // [n_amax] row maxima of |h| filled by the gate/up launch
     int n_amax;
+    // expert-parallel ownership: this device computes routed experts [ep_lo, ep_hi) and the
+    // shared expert for tokens [home_lo, home_lo + home_n); other slots are planned with 0 rows
+    int ep_lo, ep_hi, home_lo, home_n;
 };
 
 // Per-expert device pointers, indexed by expert id; entry E is the shared expert.
@@ -965,8 +968,10 @@ __device__ __forceinline__ void route_plan_body(const float *__restrict__ logits
         g.b = ex.up;
         g.a_rs = ex.gate_rs;
         g.b_rs = ex.up_rs;
-        g.row0 = sh ? routed_pairs : row0[p];
-        g.nrows = sh ? M : cnt[union_s[p]];
+        const int e_id = sh ? E : union_s[p];
+        const bool owned = sh || (e_id >= plan.ep_lo && e_id < plan.ep_hi);
+        g.row0 = sh ? routed_pairs + plan.home_lo : row0[p];
+        g.nrows = sh ? plan.home_n : (owned ? cnt[e_id] : 0);
         d = g;
         d.a = ex.down;
         d.b = nullptr;
@@ -1302,8 +1307,10 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
 // expert's row is added as out = out + (w * y) in batch-union order, the shared
 // expert's row is added last without a weight.
 __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ y, long long ldy, int D, int k,
-                                                      RoutePlan plan, float *__restrict__ out, long long ldo) {
-    const int s = blockIdx.y;
+                                                      RoutePlan plan, float *__restrict__ out, long long ldo,
+                                                      int first_token) {
+    // output row blockIdx.y holds token first_token + blockIdx.y
+    const int s = first_token + blockIdx.y;
     const int d = blockIdx.x * blockDim.x + threadIdx.x;
     if (d >= D) return;
     const int ke = plan.keff[s];
@@ -1314,7 +1321,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
     }
     const int sp0 = *plan.shared_pair0;
     if (sp0 >= 0) acc = __fadd_rn(acc, y[(long long)(sp0 + s) * ldy + d]);
-    out[(long long)s * ldo + d] = acc;
+    out[(long long)blockIdx.y * ldo + d] = acc;
 }
 
 // CSR combine of the host-pointer ABI (out[s] = sum over the row's listed y-rows

@@ -43,7 +43,8 @@ SYMBOLS = [
     "coli_cuda_tensor_upload_grouped", "coli_cuda_moe_layer_create", "coli_cuda_moe_layer_set_expert",
     "coli_cuda_moe_layer_free", "coli_cuda_moe_layer_forward_dev", "coli_cuda_moe_layer_forward",
     "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_last_pairs",
-    "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_profile", "coli_cuda_moe_layer_profile",
+    "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_moe_layer_ep_partial_dev",
+    "coli_cuda_moe_layer_ep_combine_dev", "coli_cuda_moe_layer_set_profile", "coli_cuda_moe_layer_profile",
     "coli_cuda_pipe_gemm_noalloc", "coli_cuda_last_device_error", "coli_cuda_kernel_launches", "coli_cuda_stream",
 ]
 
@@ -121,6 +122,9 @@ def lib():
         L.coli_cuda_moe_layer_enable_taps.argtypes = [vp, i]
         L.coli_cuda_moe_layer_last_pairs.argtypes = [vp, vp, vp, vp, i]
         L.coli_cuda_moe_layer_read_taps.argtypes = [vp, vp, sz, vp, sz]
+        L.coli_cuda_moe_layer_set_ep.argtypes = [vp, i, i]
+        L.coli_cuda_moe_layer_ep_partial_dev.argtypes = [vp, vp, vp, i]
+        L.coli_cuda_moe_layer_ep_combine_dev.argtypes = [vp, vp, vp, i, i, i]
         L.coli_cuda_moe_layer_set_profile.argtypes = [vp, i]
         L.coli_cuda_moe_layer_profile.argtypes = [vp, vp, vp]
         L.coli_cuda_last_device_error.argtypes = [i]
@@ -488,6 +492,27 @@ class MoeLayer:
         if lib().coli_cuda_moe_layer_read_taps(self.handle, _ptr(gu), gu.size, _ptr(dn), dn.size) != 1:
             raise CudaError("cuda moe_layer_read_taps failed")
         return gu, dn
+
+    # ---- expert parallelism (see include/peregrine_b200.h)
+    def set_ep(self, rank: int, world: int):
+        if lib().coli_cuda_moe_layer_set_ep(self.handle, rank, world) != 1:
+            raise CudaError("cuda moe_layer_set_ep failed")
+        self.ep_rank, self.ep_world = rank, world
+
+    def owned_experts(self):
+        world, rank = getattr(self, "ep_world", 1), getattr(self, "ep_rank", 0)
+        per = -(-self.n_experts // world)
+        return range(min(rank * per, self.n_experts), min((rank + 1) * per, self.n_experts))
+
+    def ep_partial_dev(self, y_pairs_ptr: int, x_all_ptr: int, m: int):
+        if lib().coli_cuda_moe_layer_ep_partial_dev(self.handle, C.c_void_p(y_pairs_ptr), C.c_void_p(x_all_ptr),
+                                                    m) != 1:
+            raise CudaError("cuda moe_layer_ep_partial_dev failed")
+
+    def ep_combine_dev(self, out_ptr: int, y_pairs_ptr: int, m: int, first_token: int, n_tokens: int):
+        if lib().coli_cuda_moe_layer_ep_combine_dev(self.handle, C.c_void_p(out_ptr), C.c_void_p(y_pairs_ptr), m,
+                                                    first_token, n_tokens) != 1:
+            raise CudaError("cuda moe_layer_ep_combine_dev failed")
 
     STAGES = ("qrow_x_unfused", "route", "route_plan_unfused", "gemv_gateup", "qrow_h_unfused", "gemv_down", "unused")
 
