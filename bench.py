@@ -358,13 +358,14 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                                 "simd": "avx2" if po.simd_tier() == 1 else "scalar",
                                 "sample": f"{n} decode tokens (M=1) of the same layer shape, median per-token time, "
                                           "32 distinct expert blobs on the host"}
-    ml.free()
-    cuda.shutdown()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()
         dist.destroy_process_group()
-    if rank == 0:
-        print(json.dumps(line), flush=True)
+    torch.cuda.synchronize()
+    ml.free()
+    cuda.shutdown()
 
 
 EP_BATCH = 32  # configs[4]: decode batch of the expert-parallel runs
@@ -488,12 +489,17 @@ def run_ep(args, rank: int, local_rank: int, world: int):
                 "call": "EpLayerRunner.forward on this rank's home tokens (pinned host in, host out)"},
         "gpu_launches": int(launches), "clocks": clocks.summary(),
     }
-    ml.free()
-    cuda.shutdown()
-    dist.barrier()
-    dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line), flush=True)
+    # teardown order matters: the collectives were enqueued on the backend's stream, so the process
+    # group goes first, then torch's tensors, and the backend (which owns that stream) last
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    del run, xs, flush, drain, x_dev, x_pin
+    torch.cuda.synchronize()
+    ml.free()
+    cuda.shutdown()
 
 
 def main():

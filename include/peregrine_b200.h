@@ -230,7 +230,7 @@ int coli_cuda_moe_layer_profile(ColiCudaMoeLayer *layer, double *stage_ms7, uint
  * x, row scales, block sums, slot table) is a 1 MiB array inside the library image instead
  * of cudaMalloc'ed buffers, so it calls no cudaMalloc/cudaFree: meant for a decode lane that
  * runs with VRAM fully committed to experts, or where a device-wide synchronising call is
- * not allowed.  Requests whose scratch exceeds 1 MiB (about S*I*1.13 bytes; S <= 151 at
+ * not allowed.  Requests whose scratch exceeds 1 MiB (about S*I*1.2 bytes; S <= 143 at
  * I = 6144) are refused with a message.  The first call on a device resolves the array's
  * address and should come before any stream capture; all calls on a device share the array,
  * so calls that overlap on the GPU race. */

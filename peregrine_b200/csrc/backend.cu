@@ -424,18 +424,14 @@ static int gemv_launch_r(Ctx *c, const GemvParams &P, bool grouped, int bpg, int
 }
 
 // ---- small-batch (tensor-core) variant: 3 or more rows in some slot
-static size_t mma_xs_bytes(int n_xrows, int kp, int nblk) {
-    return (((size_t)n_xrows * (kp + kMmaRowPad) + 15) & ~(size_t)15) + (size_t)n_xrows * nblk * 4 +
-           (size_t)n_xrows * 4 + 16;
-}
-
-template <int NT, bool GROUPED, int BPG, int XS, bool TAP>
-static int mma_launch_t(Ctx *c, const GemvParams &P, size_t smem) {
-    auto kfn = gemv_w4a8_mma_kernel<NT, GROUPED, BPG, XS, TAP>;
+template <int NT, bool GROUPED, int BPG, bool TAP>
+static int mma_launch_t(Ctx *c, const GemvParams &P) {
+    auto kfn = gemv_w4a8_mma_kernel<NT, GROUPED, BPG, TAP>;
+    const size_t smem = (size_t)mma_ring_bytes(NT) + kMmaBarBytes;
     static std::atomic<uint32_t> configured{0};
     const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
     if (!(configured.load() & bit)) {
-        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->smem_optin),
+        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                      "mma gemv shared-memory opt-in"))
             return 0;
         configured.fetch_or(bit);
@@ -444,22 +440,27 @@ static int mma_launch_t(Ctx *c, const GemvParams &P, size_t smem) {
 }
 
 template <int NT, bool GROUPED, int BPG>
-static int mma_launch_x(Ctx *c, const GemvParams &P, bool xs, size_t smem) {
-    if (P.tap) return xs ? mma_launch_t<NT, GROUPED, BPG, 1, true>(c, P, smem)
-                         : mma_launch_t<NT, GROUPED, BPG, 0, true>(c, P, smem);
-    return xs ? mma_launch_t<NT, GROUPED, BPG, 1, false>(c, P, smem) : mma_launch_t<NT, GROUPED, BPG, 0, false>(c, P, smem);
+static int mma_launch_x(Ctx *c, const GemvParams &P) {
+    return P.tap ? mma_launch_t<NT, GROUPED, BPG, true>(c, P) : mma_launch_t<NT, GROUPED, BPG, false>(c, P);
 }
 
 template <int NT>
-static int mma_launch_r(Ctx *c, const GemvParams &P, bool grouped, int bpg, bool xs, size_t smem) {
-    if (!grouped) return mma_launch_x<NT, false, 1>(c, P, xs, smem);
+static int mma_launch_r(Ctx *c, const GemvParams &P, bool grouped, int bpg) {
+    if (!grouped) return mma_launch_x<NT, false, 1>(c, P);
     switch (bpg) {
-        case 1: return mma_launch_x<NT, true, 1>(c, P, xs, smem);
-        case 2: return mma_launch_x<NT, true, 2>(c, P, xs, smem);
-        case 4: return mma_launch_x<NT, true, 4>(c, P, xs, smem);
-        case 8: return mma_launch_x<NT, true, 8>(c, P, xs, smem);
+        case 1: return mma_launch_x<NT, true, 1>(c, P);
+        case 2: return mma_launch_x<NT, true, 2>(c, P);
+        case 4: return mma_launch_x<NT, true, 4>(c, P);
+        case 8: return mma_launch_x<NT, true, 8>(c, P);
     }
     return fail("w4a8 mma gemv: unsupported group size");
+}
+
+// Rows per expert beyond which the tensor-core kernel (and the chunk-major activation layout) is used.
+static bool gemv_uses_mma(int max_rows) { return max_rows > 2; }
+// Bytes of the quantised activations of `rows` rows in the layout the kernel for `max_rows` reads.
+static size_t act_xq_bytes(const W4Layout &L, size_t rows, int max_rows) {
+    return gemv_uses_mma(max_rows) ? (size_t)L.nchunk * rows * kXqChunkRowBytes : rows * (size_t)L.kp;
 }
 
 // True when the launch's activation rows fit in shared memory beside the rings of the dp4a kernel.
@@ -489,14 +490,11 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
     P.cs_stride = L.nblk;
     P.err = c->err_dev;
     const bool grouped = L.grouped != 0;
-    if (max_rows > 2) {
+    if (gemv_uses_mma(max_rows)) {
         if (want_quant_stage) return fail("w4a8 gemv: quantising stage is not available beyond 2 rows per expert");
-        const size_t base = (size_t)kMmaRingBytes + kMmaBarBytes;
-        const size_t need = mma_xs_bytes(P.n_xrows, L.kp, L.nblk);
-        const bool xs = base + need + 1024 <= c->smem_optin;
-        const size_t smem = base + (xs ? need : 0);
-        if (max_rows <= 8) return mma_launch_r<1>(c, P, grouped, L.bpg, xs, smem);
-        return mma_launch_r<2>(c, P, grouped, L.bpg, xs, smem);
+        if (P.pcap <= 0) return fail("w4a8 gemv: the tensor-core kernel needs chunk-major activations");
+        if (max_rows <= 8) return mma_launch_r<1>(c, P, grouped, L.bpg);
+        return mma_launch_r<2>(c, P, grouped, L.bpg);
     }
     const size_t base = (size_t)kRingBytes + kGemvBarBytes;
     const bool fit = gemv_rows_fit(c, P.n_xrows, L);
@@ -507,11 +505,15 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
     return gemv_launch_r<2>(c, P, grouped, L.bpg, xs, smem);
 }
 
+// Quantises `grid_rows` (at most) fp32 rows.  pcap > 0 writes the chunk-major layout with that row
+// capacity (tensor-core kernel), else the row-major layout (dp4a kernel).  rowmap (device, optional)
+// names the source row of each output row.
 static int qrow_run(Ctx *c, const float *x, long long ldx, int K, const W4Layout &L, int8_t *xq, float *sx, int *cs,
-                    const int *n_rows_dev, int n_rows, int grid_rows) {
+                    const int *n_rows_dev, int n_rows, int grid_rows, const int *rowmap = nullptr,
+                    long long pcap = 0) {
     if (grid_rows < 1) return 1;
     return launch(qrow_i8_kernel, dim3(grid_rows), dim3(256), 0, c->stream, "activation quantise launch", x, ldx, K,
-                  L.kp, L.nblk, xq, sx, cs, n_rows_dev, n_rows);
+                  L.kp, L.nblk, xq, sx, cs, n_rows_dev, n_rows, rowmap, pcap);
 }
 
 // ------------------------------------------------------------- expert group
@@ -565,8 +567,8 @@ static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const
     // grouped formats may pad K up to a multiple of gs: size for the largest gs (256)
     const size_t kpx = ((size_t)D + 255) / 256 * 256 + 256, kph = ((size_t)I + 255) / 256 * 256 + 256;
     if (!reserve(c, c->x, xb) || !reserve(c, c->y, xb) || !reserve(c, c->h, hb) ||
-        !reserve(c, c->xq, (size_t)total * kpx) || !reserve(c, c->sx, (size_t)total * 4) ||
-        !reserve(c, c->xcs, (size_t)total * (kpx / 32) * 4) || !reserve(c, c->hq, (size_t)total * kph) ||
+        !reserve(c, c->xq, (size_t)total * kpx * 17 / 16 + 512) || !reserve(c, c->sx, (size_t)total * 4) ||
+        !reserve(c, c->xcs, (size_t)total * (kpx / 32) * 4) || !reserve(c, c->hq, (size_t)total * kph * 17 / 16 + 512) ||
         !reserve(c, c->sh, (size_t)total * 4) || !reserve(c, c->hcs, (size_t)total * (kph / 32) * 4) ||
         !reserve(c, c->slots_gu, (size_t)count * sizeof(GemvSlot)) ||
         !reserve(c, c->slots_dn, (size_t)count * sizeof(GemvSlot)) ||
@@ -622,7 +624,7 @@ static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const
                          "group slot upload") &&
                  cuda_ok(cudaMemcpy(c->nslots.p, &n, sizeof(int), cudaMemcpyHostToDevice), "group slot count") &&
                  qrow_run(c, (const float *)c->x.p, D, D, L, (int8_t *)c->xq.p, (float *)c->sx.p, (int *)c->xcs.p,
-                          nullptr, total, total);
+                          nullptr, total, total, nullptr, gemv_uses_mma(cls_max) ? total : 0);
             GemvParams P{};
             P.slots = (const GemvSlot *)c->slots_gu.p;
             P.n_slots = (const int *)c->nslots.p;
@@ -631,6 +633,7 @@ static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const
             P.sx = (const float *)c->sx.p;
             P.rowmap = nullptr;
             P.n_xrows = total;
+            P.pcap = total;
             P.out = (float *)c->h.p;
             P.out_stride = I;
             ok = ok && gemv_run(c, P, L, 0, cls_max);
@@ -670,7 +673,7 @@ static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const
                          "group slot upload") &&
                  cuda_ok(cudaMemcpy(c->nslots.p, &n, sizeof(int), cudaMemcpyHostToDevice), "group slot count") &&
                  qrow_run(c, (const float *)c->h.p, I, I, L, (int8_t *)c->hq.p, (float *)c->sh.p, (int *)c->hcs.p,
-                          nullptr, total, total);
+                          nullptr, total, total, nullptr, gemv_uses_mma(cls_max) ? total : 0);
             GemvParams P{};
             P.slots = (const GemvSlot *)c->slots_dn.p;
             P.n_slots = (const int *)c->nslots.p;
@@ -679,6 +682,7 @@ static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const
             P.sx = (const float *)c->sh.p;
             P.rowmap = nullptr;
             P.n_xrows = total;
+            P.pcap = total;
             P.out = (float *)c->y.p;
             P.out_stride = D;
             ok = ok && gemv_run(c, P, L, 1, cls_max);

@@ -63,18 +63,26 @@ __device__ __forceinline__ float silu32(float v) { return __fdiv_rn(v, __fadd_rn
 enum : int { kErrNone = 0, kErrBarrierTimeout = 1 };
 
 // ------------------------------------------------------- activation quantiser
+// Layout of the quantised activations a launch consumes.
+//   row-major  (dp4a kernel): xq[row][kp], csum[row][nblk]
+//   chunk-major (tensor-core kernel): xq[chunk][pcap][272] (256 bytes of the chunk + 16 bytes of
+//     skew so that 8 consecutive rows land on distinct shared-memory banks), csum[chunk][pcap][8];
+//     the rows of one expert are consecutive, so one bulk copy fetches a pass's rows of a chunk.
+constexpr int kXqChunkRowBytes = kChunkElems + 16;
+
 // crates/peregrine-kernels/src/quant.rs:14-33, one CTA per row.  Besides the
-// int8 row (zero padded to `kp`) and its scale it writes, per 32-element block,
+// int8 row (zero padded) and its scale it writes, per 32-element block,
 // -8 * sum(q): the term that turns the stream's stored nibbles (v+8) back into
-// signed weights inside the integer dot.
+// signed weights inside the integer dot.  `rowmap` (optional) names the source row
+// of output row r; `pcap` > 0 selects the chunk-major layout with that row capacity.
 __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ x, long long ldx, int K, int kp,
                                                       int nblk, int8_t *__restrict__ xq, float *__restrict__ sx,
                                                       int *__restrict__ csum, const int *__restrict__ n_rows_dev,
-                                                      int n_rows) {
+                                                      int n_rows, const int *__restrict__ rowmap, long long pcap) {
     const int row = blockIdx.x;
     const int limit = n_rows_dev ? *n_rows_dev : n_rows;
     if (row >= limit) return;
-    const float *xr = x + (long long)row * ldx;
+    const float *xr = x + (long long)(rowmap ? rowmap[row] : row) * ldx;
     __shared__ float red[8];
     __shared__ float s_inv;
     float amax = 0.0f;
@@ -107,10 +115,16 @@ __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ 
             q = __float2int_rn(__fmul_rn(xr[i], inv));
             q = max(-128, min(127, q));
         }
-        xq[(long long)row * kp + i] = (int8_t)q;
         int sum = q;
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (lane == 0) csum[(long long)row * nblk + blk] = -8 * sum;
+        if (pcap > 0) {
+            const long long cr = (long long)(blk >> 3) * pcap + row;
+            xq[cr * kXqChunkRowBytes + (blk & 7) * 32 + lane] = (int8_t)q;
+            if (lane == 0) csum[cr * kChunkBlocks + (blk & 7)] = -8 * sum;
+        } else {
+            xq[(long long)row * kp + i] = (int8_t)q;
+            if (lane == 0) csum[(long long)row * nblk + blk] = -8 * sum;
+        }
     }
 }
 
@@ -167,6 +181,7 @@ struct GemvParams {
     const float *sx;   // activation row scales
     const int *rowmap; // activation row of pair p (nullptr: p itself)
     int n_xrows;       // activation rows staged in shared memory (XS kernels)
+    long long pcap;    // row capacity of the chunk-major activation layout (tensor-core kernel)
     // QS kernels quantise the activation rows themselves while staging them:
     const float *x_f32;   // [n_xrows, K] fp32 rows (row stride x_ld)
     long long x_ld;

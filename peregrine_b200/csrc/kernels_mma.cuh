@@ -20,11 +20,15 @@
 namespace pgb {
 
 constexpr int kMmaWarps = 8;
-constexpr int kMmaStages = 3;
 constexpr int kMmaThreads = kMmaWarps * 32;
-constexpr int kMmaRingBytes = kMmaWarps * kMmaStages * kStageBytes;
-constexpr int kMmaBarBytes = ((kMmaWarps * kMmaStages * 8 + 127) / 128) * 128;
-constexpr int kMmaRowPad = 16;  // bytes of skew per staged activation row (bank spread for the B loads)
+// a stage holds two 16-row weight chunks, the pass's activation rows of the same chunk
+// (chunk-major layout, 272 bytes per row) and their 8 block sums each
+__host__ __device__ constexpr int mma_stages(int nt) { return nt == 1 ? 3 : 2; }
+__host__ __device__ constexpr int mma_stage_bytes(int nt) {
+    return kStageBytes + 8 * nt * kXqChunkRowBytes + 8 * nt * kChunkBlocks * 4;
+}
+__host__ __device__ constexpr int mma_ring_bytes(int nt) { return kMmaWarps * mma_stages(nt) * mma_stage_bytes(nt); }
+constexpr int kMmaBarBytes = ((kMmaWarps * 3 * 8 + 127) / 128) * 128;
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -34,27 +38,26 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// NT = 8-row activation groups per pass (rows per pass = 8 * NT).
-// XS = 0: activation rows read from global memory; 1: int8 rows copied to shared memory.
-template <int NT, bool GROUPED, int BPG, int XS, bool TAP>
+// NT = 8-row activation groups per pass (rows per pass = 8 * NT).  Activations come in the
+// chunk-major layout (kernels.cuh, qrow_i8_kernel): P.xq[chunk][pcap][272], P.csum[chunk][pcap][8],
+// P.sx[row]; rows are indexed by pair row (row0 + i), P.rowmap is not used.
+template <int NT, bool GROUPED, int BPG, bool TAP>
 __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const GemvParams P) {
     constexpr int RMAX = 8 * NT;
+    constexpr int STAGES = mma_stages(NT);
+    constexpr int STAGE_BYTES = mma_stage_bytes(NT);
+    constexpr int X_OFF = kStageBytes, CS_OFF = kStageBytes + RMAX * kXqChunkRowBytes;
     constexpr int GPC = kChunkBlocks / BPG;
     constexpr int CHUNK_BYTES = kChunkSlabBytes + (GROUPED ? GPC * 64 : 0);
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    uint8_t *ring = smem + warp * (kMmaStages * kStageBytes);
+    uint8_t *ring = smem + warp * (STAGES * STAGE_BYTES);
     const uint32_t ring_u32 = smem_u32(ring);
-    const uint32_t bar_u32 = smem_u32(smem + kMmaRingBytes) + warp * (kMmaStages * 8);
-    int8_t *xs = reinterpret_cast<int8_t *>(smem + kMmaRingBytes + kMmaBarBytes);
-    const int xs_stride = P.xq_stride + kMmaRowPad;
-    const int xs_bytes = (P.n_xrows * xs_stride + 15) & ~15;
-    int *cs_s = reinterpret_cast<int *>(xs + xs_bytes);
-    float *sx_s = reinterpret_cast<float *>(cs_s + P.n_xrows * P.cs_stride);
+    const uint32_t bar_u32 = smem_u32(smem + mma_ring_bytes(NT)) + warp * (STAGES * 8);
 
     if (lane == 0) {
-        for (int s = 0; s < kMmaStages; ++s) mbar_init(bar_u32 + s * 8, 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + s * 8, 1);
         fence_mbar_init();
         fence_proxy_async();
     }
@@ -73,48 +76,33 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
     uint32_t fq = 0, cq = 0;
 
     auto issue = [&](const TileCursor &c, uint32_t q) {
-        const uint32_t stage = q % kMmaStages;
+        const uint32_t stage = q % STAGES;
         const uint32_t bar = bar_u32 + stage * 8;
-        const uint32_t dst = ring_u32 + stage * kStageBytes;
+        const uint32_t dst = ring_u32 + stage * STAGE_BYTES;
         const size_t off = (size_t)c.chunk * CHUNK_BYTES;
-        mbar_expect_tx(bar, c.b ? 2 * CHUNK_BYTES : CHUNK_BYTES);
+        const int first = c.row0 + c.pass * RMAX;
+        const int nr = min(RMAX, c.nrows - c.pass * RMAX);
+        const long long cr = (long long)c.chunk * P.pcap + first;
+        mbar_expect_tx(bar, (c.b ? 2 * CHUNK_BYTES : CHUNK_BYTES) + nr * (kXqChunkRowBytes + kChunkBlocks * 4));
         bulk_g2s(dst, c.a + off, CHUNK_BYTES, bar);
         if (c.b) bulk_g2s(dst + kChunkMaxBytes, c.b + off, CHUNK_BYTES, bar);
+        bulk_g2s(dst + X_OFF, P.xq + cr * kXqChunkRowBytes, nr * kXqChunkRowBytes, bar);
+        bulk_g2s(dst + CS_OFF, P.csum + cr * kChunkBlocks, nr * kChunkBlocks * 4, bar);
     };
-    while (fc.i < total && fq < cq + kMmaStages) {
+    while (fc.i < total && fq < cq + STAGES) {
         if (lane == 0) issue(fc, fq);
         cursor_next<RMAX>(fc, P, total, stride);
         ++fq;
     }
 
-    if (XS == 1) {
-        // row by row: the shared-memory rows carry a 16-byte skew
-        const int v_per_row = P.xq_stride >> 4;
-        for (int i = threadIdx.x; i < P.n_xrows * v_per_row; i += blockDim.x) {
-            const int row = i / v_per_row, v = i - row * v_per_row;
-            *reinterpret_cast<uint4 *>(xs + (size_t)row * xs_stride + 16 * v) =
-                *reinterpret_cast<const uint4 *>(P.xq + (size_t)row * P.xq_stride + 16 * v);
-        }
-        const int ncs = P.n_xrows * P.cs_stride;
-        for (int i = threadIdx.x; i < ncs; i += blockDim.x) cs_s[i] = P.csum[i];
-        for (int i = threadIdx.x; i < P.n_xrows; i += blockDim.x) sx_s[i] = P.sx[i];
-        __syncthreads();
-    }
-    const int8_t *xbase = XS ? xs : P.xq;
-    const int xstride = XS ? xs_stride : P.xq_stride;
-    const int *csbase = XS ? cs_s : P.csum;
-    const float *sxbase = XS ? sx_s : P.sx;
-
     // accumulators: [half][n-tile][fragment slot]; slot i: row g + 8*(i>>1), column 2t + (i&1)
     float acc[2][NT][4];
     int iacc[2][NT][4];
     int csacc[NT][2];   // per-row format: running -8*sum over the whole K, columns 2t, 2t+1
-    int arow_b[NT];     // activation row feeding this lane's B fragment (column g of n-tile nt)
-    int arow_c[NT][2];  // activation rows of this lane's accumulator columns 2t, 2t+1
     bool failed = false;
 
     while (cc.i < total) {
-        if (fc.i < total && fq < cq + kMmaStages) {
+        if (fc.i < total && fq < cq + STAGES) {
             if (lane == 0) {
                 fence_proxy_async();
                 issue(fc, fq);
@@ -122,8 +110,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
             cursor_next<RMAX>(fc, P, total, stride);
             ++fq;
         }
-        const uint32_t stage = cq % kMmaStages;
-        const uint32_t parity = (cq / kMmaStages) & 1u;
+        const uint32_t stage = cq % STAGES;
+        const uint32_t parity = (cq / STAGES) & 1u;
         {
             const bool ok = mbar_wait_bounded(bar_u32 + stage * 8, parity);
             if (__any_sync(0xffffffffu, !ok)) {
@@ -143,16 +131,9 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                         iacc[h][nt][i] = 0;
                     }
                 csacc[nt][0] = csacc[nt][1] = 0;
-                const int rb = min(cc.pass * RMAX + 8 * nt + g, cc.nrows - 1);
-                arow_b[nt] = P.rowmap ? P.rowmap[cc.row0 + rb] : cc.row0 + rb;
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const int rc = min(cc.pass * RMAX + 8 * nt + 2 * t + j, cc.nrows - 1);
-                    arow_c[nt][j] = P.rowmap ? P.rowmap[cc.row0 + rc] : cc.row0 + rc;
-                }
             }
         }
-        const uint8_t *st = ring + stage * kStageBytes;
+        const uint8_t *st = ring + stage * STAGE_BYTES;
 #pragma unroll
         for (int gi = 0; gi < GPC; ++gi) {
             int c[2][NT][4];
@@ -171,19 +152,13 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                 uint32_t b0[NT], b1[NT];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    const int8_t *xr = xbase + (size_t)arow_b[nt] * xstride + cc.chunk * kChunkElems + blk * 32 + 4 * t;
-                    if (XS) {
-                        b0[nt] = *reinterpret_cast<const uint32_t *>(xr);
-                        b1[nt] = *reinterpret_cast<const uint32_t *>(xr + 16);
-                    } else {
-                        b0[nt] = __ldg(reinterpret_cast<const uint32_t *>(xr));
-                        b1[nt] = __ldg(reinterpret_cast<const uint32_t *>(xr + 16));
-                    }
+                    // columns past the pass's rows read stale shared memory: their results are never stored
+                    const uint8_t *xr = st + X_OFF + (8 * nt + g) * kXqChunkRowBytes + blk * 32 + 4 * t;
+                    b0[nt] = *reinterpret_cast<const uint32_t *>(xr);
+                    b1[nt] = *reinterpret_cast<const uint32_t *>(xr + 16);
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int *cp = csbase + (size_t)arow_c[nt][j] * P.cs_stride + cc.chunk * kChunkBlocks + blk;
-                        csg[nt][j] += XS ? *cp : __ldg(cp);
-                    }
+                    for (int j = 0; j < 2; ++j)
+                        csg[nt][j] += *reinterpret_cast<const int *>(st + CS_OFF + ((8 * nt + 2 * t + j) * kChunkBlocks + blk) * 4);
                 }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -237,7 +212,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
         if (cc.chunk == P.nchunk - 1) {
             // value of accumulator slot (h, nt, i) after the activation scale
             auto value = [&](int h, int nt, int i, int o) -> float {
-                const float sxa = sxbase[arow_c[nt][i & 1]];
+                const int rr = min(cc.pass * RMAX + 8 * nt + 2 * t + (i & 1), cc.nrows - 1);
+                const float sxa = P.sx[cc.row0 + rr];
                 if (GROUPED) return __fmul_rn(acc[h][nt][i], sxa);
                 const float *rsp = (P.mode == 0 && h) ? cc.b_rs : cc.a_rs;
                 const float rs = (o < P.ntile * 16) ? rsp[o] : 0.0f;
@@ -325,7 +301,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
     }
     if (failed) {
         for (uint32_t q = cq; q < fq; ++q) {
-            const uint32_t stage = q % kMmaStages, parity = (q / kMmaStages) & 1u;
+            const uint32_t stage = q % STAGES, parity = (q / STAGES) & 1u;
             const long long t0 = clock64();
             while (!mbar_try_wait(bar_u32 + stage * 8, parity))
                 if (clock64() - t0 > 200000000LL) break;
