@@ -202,6 +202,14 @@ int coli_cuda_moe_layer_last_pairs(ColiCudaMoeLayer *layer, int *n_pairs, int *p
 int coli_cuda_moe_layer_read_taps(ColiCudaMoeLayer *layer, int32_t *gateup_taps, size_t gateup_count,
                                   int32_t *down_taps, size_t down_count);
 
+/* Two device-pointer primitives the decode loop around the FFN needs, in the style of the pipe_* family
+ * (no counterpart in cuda/backend_cuda.h; the reference does both on the host):
+ * embedding row gather x_dev[s,:] = table_dev[ids_dev[s],:] (fp32 table [V, D]) and greedy
+ * pick ids_dev[s] = argmax(logits_dev[s,:V]) with the rules of crates/peregrine-model/src/sample.rs:21-32
+ * (first non-NaN start, strict '>', lowest index wins, all-NaN row -> 0). */
+int coli_cuda_pipe_embed(int device, float *x_dev, const float *table_dev, const int *ids_dev, int S, int D, int V);
+int coli_cuda_pipe_argmax(int device, int *ids_dev, const float *logits_dev, int S, int V);
+
 /* Expert parallelism over the GPUs of one node (the reference has none: crates/peregrine-model/src/gpu.rs:1454-1457
  * hard-codes one device; docs/scale-out-design.md:34-72 sketches an owner map per (layer, expert) and requires
  * cross-device partial sums in fixed order).  Rank r of `world` owns the routed experts

@@ -45,7 +45,7 @@ SYMBOLS = [
     "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_last_pairs",
     "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_moe_layer_ep_partial_dev",
     "coli_cuda_moe_layer_ep_combine_dev", "coli_cuda_moe_layer_set_profile", "coli_cuda_moe_layer_profile",
-    "coli_cuda_pipe_gemm_noalloc", "coli_cuda_last_device_error", "coli_cuda_kernel_launches", "coli_cuda_stream",
+    "coli_cuda_pipe_gemm_noalloc", "coli_cuda_pipe_embed", "coli_cuda_pipe_argmax", "coli_cuda_last_device_error", "coli_cuda_kernel_launches", "coli_cuda_stream",
 ]
 
 
@@ -104,6 +104,8 @@ def lib():
         L.coli_cuda_pipe_rows_add.argtypes = [i, vp, vp, vp, i, i]
         L.coli_cuda_pipe_gemm.argtypes = [vp, vp, vp, i]
         L.coli_cuda_pipe_gemm_noalloc.argtypes = [vp, vp, vp, i]
+        L.coli_cuda_pipe_embed.argtypes = [i, vp, vp, vp, i, i, i]
+        L.coli_cuda_pipe_argmax.argtypes = [i, vp, vp, i, i]
         L.coli_cuda_pipe_copy2d.argtypes = [i, vp, i, vp, i, i, i]
         L.coli_cuda_pipe_peer_copy.argtypes = [i, vp, i, vp, sz]
         L.coli_cuda_pipe_sync.argtypes = [i]

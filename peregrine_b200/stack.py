@@ -1,0 +1,148 @@
+"""Synthetic FFN-only decode stack (BASELINE.json configs[4] shape family) on one device.
+
+    embed -> [ rmsnorm -> (dense SwiGLU | MoE layer) -> residual add ] x L -> rmsnorm -> lm_head -> argmax
+
+This is the loop shape of the reference's batched decode step with attention left out
+(crates/peregrine-model/src/model.rs:1971-2006 per layer, :4260-4261 final norm + lm_head,
+sample.rs:21-43 greedy pick).  Everything stays on the device between steps: token ids feed
+the next step's embedding gather without a host round trip.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import cuda
+from .resident import upload_expert, upload_layer
+from .synth import SynthExpert, SynthLayer, SynthMatrix, synth_expert, synth_layer, synth_matrix
+
+
+@dataclass
+class SynthStack:
+    hidden: int
+    vocab: int
+    eps: float
+    embed: np.ndarray                  # fp32 [vocab, hidden]
+    norms: list                        # per layer fp32 [hidden]
+    final_norm: np.ndarray
+    lm_head: SynthMatrix               # int4 [vocab, hidden]
+    layers: list = field(default_factory=list)   # SynthExpert (dense) or SynthLayer (MoE)
+
+
+def synth_stack(seed: int, hidden: int, inter: int, dense_inter: int, n_experts: int, k: int, n_layers: int,
+                first_dense: int, vocab: int, gs: int = 32, distinct_experts: int | None = None) -> SynthStack:
+    rng = np.random.default_rng(seed)
+    embed = rng.standard_normal((vocab, hidden)).astype(np.float32)
+    norms = [(1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32) for _ in range(n_layers)]
+    final_norm = (1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)
+    lm_head = synth_matrix(rng, vocab, hidden, gs)
+    layers = []
+    for li in range(n_layers):
+        if li < first_dense:
+            layers.append(synth_expert(rng, hidden, dense_inter, gs))
+        else:
+            layers.append(synth_layer(seed * 1000 + li, hidden, inter, n_experts, k, gs, shared=True,
+                                      distinct_experts=distinct_experts))
+    return SynthStack(hidden, vocab, 1e-5, embed, norms, final_norm, lm_head, layers)
+
+
+class _DevBuf:
+    def __init__(self, device: int, host: np.ndarray | None = None, nbytes: int | None = None):
+        self.device = device
+        self.nbytes = host.nbytes if host is not None else nbytes
+        self.ptr = cuda.lib().coli_cuda_pipe_alloc(device, self.nbytes)
+        if not self.ptr:
+            raise cuda.CudaError("device allocation failed")
+        if host is not None:
+            host = np.ascontiguousarray(host)
+            if cuda.lib().coli_cuda_pipe_upload(device, self.ptr, host.ctypes.data, host.nbytes) != 1:
+                raise cuda.CudaError("device upload failed")
+
+    def download(self, shape, dtype):
+        out = np.empty(shape, dtype)
+        if cuda.lib().coli_cuda_pipe_download(self.device, self.ptr, out.ctypes.data, out.nbytes) != 1:
+            raise cuda.CudaError("device download failed")
+        return out
+
+    def free(self):
+        if self.ptr:
+            cuda.lib().coli_cuda_pipe_free(self.device, self.ptr)
+            self.ptr = None
+
+
+class DeviceStack:
+    """The stack resident on one device; ``decode`` runs greedy steps without host round trips."""
+
+    def __init__(self, device: int, st: SynthStack, batch: int, max_steps: int):
+        L = cuda.lib()
+        self.device, self.st, self.batch, self.max_steps = device, st, batch, max_steps
+        self.embed = _DevBuf(device, st.embed)
+        self.norms = [_DevBuf(device, w) for w in st.norms]
+        self.final_norm = _DevBuf(device, st.final_norm)
+        self.lm_head = cuda.Tensor.upload_grouped(device, st.lm_head.q, st.lm_head.scale, st.hidden, st.vocab,
+                                                  st.lm_head.gs)
+        self.layers = []
+        for layer in st.layers:
+            if isinstance(layer, SynthLayer):
+                self.layers.append(upload_layer(device, layer))
+            else:
+                self.layers.append(upload_expert(device, layer, st.hidden, layer.gate.o_n))
+        d, b = st.hidden, batch
+        widest = max([l.gate.o_n for l in st.layers if isinstance(l, SynthExpert)] + [1])
+        self.x = _DevBuf(device, nbytes=b * d * 4)
+        self.nrm = _DevBuf(device, nbytes=b * d * 4)
+        self.ffn = _DevBuf(device, nbytes=b * d * 4)
+        self.g = _DevBuf(device, nbytes=b * widest * 4)
+        self.u = _DevBuf(device, nbytes=b * widest * 4)
+        self.logits = _DevBuf(device, nbytes=b * st.vocab * 4)
+        self.ids = _DevBuf(device, nbytes=(max_steps + 1) * b * 4)
+        self._L = L
+
+    def _ok(self, rc, what):
+        if rc != 1:
+            raise cuda.CudaError(f"stack: {what} failed")
+
+    def step(self, t: int):
+        """ids[t] -> ids[t+1], all on the device's stream."""
+        L, dev, st, b, d = self._L, self.device, self.st, self.batch, self.st.hidden
+        vp = C.c_void_p
+        ids_in = vp(self.ids.ptr + t * b * 4)
+        ids_out = vp(self.ids.ptr + (t + 1) * b * 4)
+        self._ok(L.coli_cuda_pipe_embed(dev, vp(self.x.ptr), vp(self.embed.ptr), ids_in, b, d, st.vocab), "embed")
+        for li, layer in enumerate(self.layers):
+            self._ok(L.coli_cuda_pipe_rmsnorm(dev, vp(self.nrm.ptr), vp(self.x.ptr), vp(self.norms[li].ptr), b, d,
+                                              C.c_float(st.eps)), "rmsnorm")
+            if isinstance(layer, cuda.MoeLayer):
+                layer.forward_dev(self.ffn.ptr, self.nrm.ptr, b)
+            else:
+                inter = layer.gate.o_n
+                self._ok(L.coli_cuda_pipe_gemm(layer.gate.handle, vp(self.g.ptr), vp(self.nrm.ptr), b), "gate")
+                self._ok(L.coli_cuda_pipe_gemm(layer.up.handle, vp(self.u.ptr), vp(self.nrm.ptr), b), "up")
+                self._ok(L.coli_cuda_pipe_silu_mul(dev, vp(self.g.ptr), vp(self.u.ptr), b * inter), "silu_mul")
+                self._ok(L.coli_cuda_pipe_gemm(layer.down.handle, vp(self.ffn.ptr), vp(self.g.ptr), b), "down")
+            self._ok(L.coli_cuda_pipe_add(dev, vp(self.x.ptr), vp(self.ffn.ptr), b * d), "residual")
+        self._ok(L.coli_cuda_pipe_rmsnorm(dev, vp(self.nrm.ptr), vp(self.x.ptr), vp(self.final_norm.ptr), b, d,
+                                          C.c_float(st.eps)), "final rmsnorm")
+        self._ok(L.coli_cuda_pipe_gemm(self.lm_head.handle, vp(self.logits.ptr), vp(self.nrm.ptr), b), "lm_head")
+        self._ok(L.coli_cuda_pipe_argmax(dev, ids_out, vp(self.logits.ptr), b, st.vocab), "argmax")
+
+    def decode(self, ids0: np.ndarray, steps: int) -> np.ndarray:
+        """Greedy decode: returns int32 ids [steps, batch] (the tokens picked at each step)."""
+        if steps > self.max_steps:
+            raise ValueError("more steps than the id buffer holds")
+        ids0 = np.ascontiguousarray(ids0, np.int32)
+        self._ok(self._L.coli_cuda_pipe_upload(self.device, C.c_void_p(self.ids.ptr), ids0.ctypes.data, ids0.nbytes),
+                 "ids upload")
+        for t in range(steps):
+            self.step(t)
+        return self.ids.download((steps + 1, self.batch), np.int32)[1:]
+
+    def free(self):
+        for l in self.layers:
+            l.free()
+        self.lm_head.free()
+        for b in [self.embed, self.final_norm, self.x, self.nrm, self.ffn, self.g, self.u, self.logits, self.ids] + \
+                self.norms:
+            b.free()

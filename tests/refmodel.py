@@ -25,3 +25,30 @@ def rel_err(a, b):
     a = np.asarray(a, np.float64)
     b = np.asarray(b, np.float64)
     return float(np.max(np.abs(a - b) / np.maximum(np.abs(b), 1e-6)))
+
+
+def oracle_stack_decode(st, ids0, steps, threads=4):
+    """CPU restatement of peregrine_b200.stack.DeviceStack.decode with the oracle's functions:
+    embed -> [rmsnorm -> (dense swiglu | moe_forward) -> residual] x L -> rmsnorm -> lm_head -> argmax
+    (crates/peregrine-model/src/model.rs:1971-2006, 4260-4261; sample.rs:21-43)."""
+    from peregrine_b200.synth import SynthLayer
+
+    ids = np.array(ids0, np.int32)
+    out = []
+    lm = o_weight(st.lm_head)
+    for _ in range(steps):
+        x = st.embed[ids].astype(np.float32).copy()
+        b = x.shape[0]
+        for li, layer in enumerate(st.layers):
+            nrm = np.stack([po.rmsnorm(x[s], st.norms[li], st.eps) for s in range(b)])
+            if isinstance(layer, SynthLayer):
+                ffn = oracle_layer_forward(layer, nrm, threads=threads)
+            else:
+                g, u, d = o_expert(layer)
+                ffn = po.swiglu(g, u, d, nrm, b)
+            x = (x + ffn).astype(np.float32)
+        nrm = np.stack([po.rmsnorm(x[s], st.final_norm, st.eps) for s in range(b)])
+        logits = lm.apply(nrm, b)
+        ids = np.array([po.argmax(logits[s]) for s in range(b)], np.int32)
+        out.append(ids.copy())
+    return np.stack(out)
