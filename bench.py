@@ -34,8 +34,9 @@ UNIT = "tok/s"
 N_TOKENS = 64           # distinct synthetic tokens cycled through the steps
 FLUSH_BYTES = 256 << 20  # > 126 MB L2
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up + one down GEMV launch
-# (ncu capture, see profiles/); None until a capture has been taken.
-NCU_GEMV_TRAFFIC_BYTES_PER_STEP = None
+# (ncu capture of the M = 1 step, profiles/decode_m1_layer_kernels.md):
+# gate/up 141.59 MB read + 3.53 MB written, down 70.89 MB read + 1.16 MB written.
+NCU_GEMV_TRAFFIC_BYTES_PER_STEP = 217_170_000
 
 
 def measured_peaks():

@@ -196,6 +196,13 @@ int coli_cuda_moe_layer_last_routing(ColiCudaMoeLayer *layer, int M, int *idx, f
  * coli_cuda_moe_layer_last_pairs.  For per-row (fmt 2) experts ng is 1 and the tap
  * is the whole-row accumulator. */
 int coli_cuda_moe_layer_enable_taps(ColiCudaMoeLayer *layer, int enable);
+/* Speculative routing of decode-sized batches (at most 2 tokens, one device): the expert launches
+ * start from a selection made on parallel-sum logits while the exact sequential router chains
+ * (crates/peregrine-kernels/src/matmul.rs:18-30) run beside them; weights, combine order and the
+ * selection check come from the exact chains, and a disagreement is recomputed, so results do not
+ * depend on the mode.  mode: -1 process default (on unless PEREGRINE_B200_SPEC_ROUTE=0), 0 off,
+ * 1 on, 2 on with the speculative pick deliberately wrong (exercises the recompute path). */
+int coli_cuda_moe_layer_set_spec(ColiCudaMoeLayer *layer, int mode);
 /* pair_token[p] = token of pair row p, pair_expert[p] = expert id (E = shared). */
 int coli_cuda_moe_layer_last_pairs(ColiCudaMoeLayer *layer, int *n_pairs, int *pair_token, int *pair_expert,
                                    int capacity);

@@ -28,6 +28,7 @@ struct DevBuf {
 struct Ctx {
     int device = -1;
     cudaStream_t stream = nullptr;
+    cudaStream_t side = nullptr;  // runs the exact router chains beside the speculative expert launches
     int sms = 0;
     size_t smem_optin = 0;
     size_t tensor_count = 0, tensor_bytes = 0;
@@ -152,6 +153,7 @@ PGB_EXPORT int coli_cuda_init(const int *devices, int count) {
         cudaDeviceProp prop{};
         if (!select_ctx(c) || !cuda_ok(cudaGetDeviceProperties(&prop, device), "device properties") ||
             !cuda_ok(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking), "stream creation") ||
+            !cuda_ok(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking), "stream creation") ||
             !cuda_ok(cudaMalloc(&c->err_dev, 256), "error word allocation") ||
             !cuda_ok(cudaMemset(c->err_dev, 0, 256), "error word clear")) {
             g_nctx++;
@@ -183,6 +185,7 @@ PGB_EXPORT void coli_cuda_shutdown(void) {
         for (DevBuf *b : bufs) free_buf(*b);
         for (DevBuf &b : c->pipe) free_buf(b);
         if (c->err_dev) cudaFree(c->err_dev);
+        if (c->side) cudaStreamDestroy(c->side);
         if (c->stream) cudaStreamDestroy(c->stream);
         *c = Ctx();
     }
@@ -395,7 +398,7 @@ static int gemv_launch_t(Ctx *c, const GemvParams &P, size_t smem) {
             return 0;
         configured.fetch_or(bit);
     }
-    return launch(kfn, dim3(c->sms), dim3(kGemvThreads), smem, c->stream, "w4a8 gemv launch", P);
+    return launch(kfn, dim3(P.grid > 0 ? P.grid : c->sms), dim3(kGemvThreads), smem, c->stream, "w4a8 gemv launch", P);
 }
 
 template <int RMAX, bool GROUPED, int BPG>

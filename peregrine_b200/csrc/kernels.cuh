@@ -129,8 +129,14 @@ __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ 
 }
 
 // ------------------------------------------------------------ int4 x int8 GEMV
-constexpr int kGemvWarps = 12;
-constexpr int kGemvStages = 3;
+#ifndef PGB_GEMV_WARPS
+#define PGB_GEMV_WARPS 12
+#endif
+#ifndef PGB_GEMV_STAGES
+#define PGB_GEMV_STAGES 3
+#endif
+constexpr int kGemvWarps = PGB_GEMV_WARPS;
+constexpr int kGemvStages = PGB_GEMV_STAGES;
 constexpr int kGemvThreads = kGemvWarps * 32;
 constexpr int kStageBytes = 2 * kChunkMaxBytes;  // two half-warp chunks
 constexpr int kRingBytes = kGemvWarps * kGemvStages * kStageBytes;
@@ -187,6 +193,13 @@ struct GemvParams {
     long long x_ld;
     int K;                // logical row length
     const unsigned *amax_bits;  // [n_xrows] bit pattern of max|x| per row
+    // speculative routing: the launch compares two selections (spec_n ids and spec_m counts).  Equal:
+    // a mode-0 launch has nothing to repair and returns; a mode-1 launch reads amax_bits.  Different:
+    // the mode-0 launch recomputes under its (exact) slots, the mode-1 launch reads amax_alt.
+    const int *spec_a, *spec_b, *spec_ka, *spec_kb;
+    int spec_n, spec_m;
+    const unsigned *amax_alt;
+    int grid;  // host only: CTAs to launch (0 = one per SM)
     const int *n_xrows_dev;     // rows actually valid (device scalar; nullptr: n_xrows)
     unsigned *amax_out;   // mode 0: per pair row, atomicMax of |h| bits (nullptr: off)
     float *out;
@@ -264,6 +277,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = lane >> 4, r16 = lane & 15;
+    bool spec_same = true;
+    if (P.spec_a) {
+        int bad = 0;
+        for (int i = threadIdx.x; i < P.spec_n; i += blockDim.x) bad |= (__ldcg(P.spec_a + i) != __ldcg(P.spec_b + i));
+        for (int i = threadIdx.x; i < P.spec_m; i += blockDim.x) bad |= (__ldcg(P.spec_ka + i) != __ldcg(P.spec_kb + i));
+        spec_same = __syncthreads_or(bad) == 0;
+        if (P.mode == 0 && spec_same) return;  // the speculative launch already produced these rows
+    }
     uint8_t *ring = smem + warp * (kGemvStages * kStageBytes);
     const uint32_t ring_u32 = smem_u32(ring);
     const uint32_t bar_u32 = smem_u32(smem + kRingBytes) + warp * (kGemvStages * 8);
@@ -321,7 +342,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
         const int nrows_valid = P.n_xrows_dev ? min(*P.n_xrows_dev, P.n_xrows) : P.n_xrows;
         float *inv_s = sx_s + P.n_xrows;  // scratch: 1/s per row
         for (int row = threadIdx.x; row < nrows_valid; row += blockDim.x) {
-            float s = __fdiv_rn(__uint_as_float(P.amax_bits[row]), 127.0f);
+            const unsigned *ab = (P.amax_alt && !spec_same) ? P.amax_alt : P.amax_bits;
+            float s = __fdiv_rn(__uint_as_float(ab[row]), 127.0f);
             if (s < 1e-12f) s = 1e-12f;
             sx_s[row] = s;
             inv_s[row] = __fdiv_rn(1.0f, s);
@@ -1048,46 +1070,96 @@ struct RouteArgs {
     int *xcs;
     int kp, nblk;
     int *err;
+    float spec_sign;  // route_spec_kernel: -1 turns the speculative pick upside down (repair-path self-test)
 };
+
+// Quantiser role of the routing launches (crates/peregrine-kernels/src/quant.rs:14-33): one CTA
+// turns token `row` into int8 with its scale and the -8*sum correction of every 32-block.
+__device__ __forceinline__ void route_quantise_row(const RouteArgs &A, int row, unsigned char *rt_smem) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float *xr = A.x + (long long)row * A.ldx;
+    float *red = reinterpret_cast<float *>(rt_smem);
+    const int n4 = A.D >> 2;
+    if (A.kp == A.D && (A.D & 31) == 0 && n4 <= 8 * (int)blockDim.x && (blockDim.x & 7) == 0 &&
+        ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(A.xq)) & 15) == 0) {
+        // the whole row in registers: one round trip to memory, then maximum, scale and rounding
+        // from the registers.  Eight neighbouring lanes hold one 32-element block.
+        const float4 *x4 = reinterpret_cast<const float4 *>(xr);
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = tid + u * (int)blockDim.x;
+            v[u] = i < n4 ? __ldg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (lane == 0) red[warp] = amax;
+        __syncthreads();
+        float m = red[0];
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+        float s = __fdiv_rn(m, 127.0f);
+        if (s < 1e-12f) s = 1e-12f;
+        const float inv = __fdiv_rn(1.0f, s);
+        if (tid == 0) A.sx[row] = s;
+        uint32_t *xq32 = reinterpret_cast<uint32_t *>(A.xq + (long long)row * A.kp);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = tid + u * (int)blockDim.x;
+            const int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].x, inv))));
+            const int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].y, inv))));
+            const int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].z, inv))));
+            const int q3 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].w, inv))));
+            if (i < n4)
+                xq32[i] = (uint32_t)(q0 & 255) | ((uint32_t)(q1 & 255) << 8) | ((uint32_t)(q2 & 255) << 16) |
+                          ((uint32_t)(q3 & 255) << 24);
+            int sum = (q0 + q1) + (q2 + q3);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            if ((lane & 7) == 0 && i < n4) A.xcs[(long long)row * A.nblk + (i >> 3)] = -8 * sum;
+        }
+        return;
+    }
+    float amax = 0.0f;
+    for (int i = tid; i < A.D; i += blockDim.x) {
+        const float a = fabsf(xr[i]);
+        if (a > amax) amax = a;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, amax, o);
+        if (other > amax) amax = other;
+    }
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    float m = red[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+        if (red[w] > m) m = red[w];
+    float s = __fdiv_rn(m, 127.0f);
+    if (s < 1e-12f) s = 1e-12f;
+    const float inv = __fdiv_rn(1.0f, s);
+    if (tid == 0) A.sx[row] = s;
+    for (int blk = warp; blk < A.nblk; blk += (int)(blockDim.x >> 5)) {
+        const int i = blk * 32 + lane;
+        int q = 0;
+        if (i < A.D) {
+            q = __float2int_rn(__fmul_rn(xr[i], inv));
+            q = max(-128, min(127, q));
+        }
+        A.xq[(long long)row * A.kp + i] = (int8_t)q;
+        int sum = q;
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) A.xcs[(long long)row * A.nblk + blk] = -8 * sum;
+    }
+}
 
 __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs A) {
     extern __shared__ __align__(128) unsigned char rt_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if ((int)blockIdx.x >= A.n_chain_ctas) {
-        // ---------------- quantiser role (crates/peregrine-kernels/src/quant.rs:14-33)
-        const int row = blockIdx.x - A.n_chain_ctas;
-        const float *xr = A.x + (long long)row * A.ldx;
-        float *red = reinterpret_cast<float *>(rt_smem);
-        float amax = 0.0f;
-        for (int i = tid; i < A.D; i += blockDim.x) {
-            const float a = fabsf(xr[i]);
-            if (a > amax) amax = a;
-        }
-        for (int o = 16; o > 0; o >>= 1) {
-            const float other = __shfl_xor_sync(0xffffffffu, amax, o);
-            if (other > amax) amax = other;
-        }
-        if (lane == 0) red[warp] = amax;
-        __syncthreads();
-        float m = red[0];
-        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-            if (red[w] > m) m = red[w];
-        float s = __fdiv_rn(m, 127.0f);
-        if (s < 1e-12f) s = 1e-12f;
-        const float inv = __fdiv_rn(1.0f, s);
-        if (tid == 0) A.sx[row] = s;
-        for (int blk = warp; blk < A.nblk; blk += (int)(blockDim.x >> 5)) {
-            const int i = blk * 32 + lane;
-            int q = 0;
-            if (i < A.D) {
-                q = __float2int_rn(__fmul_rn(xr[i], inv));
-                q = max(-128, min(127, q));
-            }
-            A.xq[(long long)row * A.kp + i] = (int8_t)q;
-            int sum = q;
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (lane == 0) A.xcs[(long long)row * A.nblk + blk] = -8 * sum;
-        }
+        route_quantise_row(A, blockIdx.x - A.n_chain_ctas, rt_smem);
         return;
     }
     // ---------------- chain role
@@ -1315,6 +1387,230 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
     __threadfence();
     route_plan_body(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts, A.plan,
                     rt_smem);
+}
+
+// Plan of a speculative selection for at most kSpecTokens tokens on one device.  Only what the
+// gate/up launch reads is produced (selection ids, pair rows, gate/up slots, cleared scratch) with
+// the numbering rules of route_plan_body, so that an agreeing exact plan describes the same rows.
+constexpr int kSpecTokens = 2;
+__device__ __forceinline__ void route_plan_small(const float *__restrict__ logits, const float *__restrict__ bias,
+                                                 int M, int E, int k, int has_shared,
+                                                 const ExpertDev *__restrict__ experts, const RoutePlan &plan,
+                                                 unsigned char *rp_smem) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned *key_all = reinterpret_cast<unsigned *>(rp_smem);        // [kSpecTokens][E]
+    int *idx_s = reinterpret_cast<int *>(key_all + kSpecTokens * E);  // [kSpecTokens][32]
+    int *keff_s = idx_s + kSpecTokens * 32;                           // [kSpecTokens]
+    for (int i = threadIdx.x; i < plan.n_col; i += blockDim.x) plan.col_done[i] = 0;
+    for (int i = threadIdx.x; i < plan.n_amax; i += blockDim.x) plan.amax[i] = 0u;
+    if (warp < M) {
+        const int s = warp;
+        unsigned *key = key_all + s * E;
+        // scores: eight experts per lane and round trip; the fast exponential is enough for a guess
+        for (int e0 = 0; e0 < E; e0 += 256) {
+            float lg[8], bs[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = e0 + u * 32 + lane;
+                lg[u] = e < E ? __ldcg(logits + (long long)s * E + e) : 0.0f;
+                bs[u] = e < E ? __ldg(bias + e) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = e0 + u * 32 + lane;
+                const float c = __fdividef(1.0f, 1.0f + __expf(-lg[u])) + bs[u];
+                unsigned q = 0u;
+                if (c > -INFINITY) {
+                    q = __float_as_uint(c == 0.0f ? 0.0f : c);
+                    q = (q & 0x80000000u) ? ~q : (q | 0x80000000u);
+                }
+                if (e < E) key[e] = q;
+            }
+        }
+        __syncwarp();
+        int kept = k;
+        for (int kk = 0; kk < k; ++kk) {
+            unsigned bu = 0u;
+            int bi = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const unsigned u = key[e];
+                if (u > bu) {
+                    bu = u;
+                    bi = e;
+                }
+            }
+            const unsigned top = __reduce_max_sync(0xffffffffu, bu);
+            if (top == 0u) {
+                kept = kk;
+                break;
+            }
+            const int best = (int)__reduce_min_sync(0xffffffffu, (unsigned)(bu == top ? bi : 0x7fffffff));
+            if (lane == 0) {
+                key[best] = 0u;
+                idx_s[s * 32 + kk] = best;
+            }
+            __syncwarp();
+        }
+        if (lane < k) plan.idx[s * k + lane] = lane < kept ? idx_s[s * 32 + lane] : 0;
+        if (lane == 0) {
+            keff_s[s] = kept;
+            plan.keff[s] = kept;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // Union and pair rows for one or two tokens, lane kk = selection kk.  Token 0's picks are
+        // union slots 0..keff0-1 in order; a pick of token 1 either repeats one of them (its row
+        // follows token 0's row of that expert) or opens a new slot in kk order.
+        const int keff0 = keff_s[0], keff1 = M > 1 ? keff_s[1] : 0;
+        const int e0 = lane < keff0 ? idx_s[lane] : -1;
+        const int e1 = lane < keff1 ? idx_s[32 + lane] : -2;
+        int dup_of = -1;      // slot of token 0 that my token-1 pick repeats
+        bool shared_by_1 = false;  // my token-0 pick is repeated by token 1
+        for (int j = 0; j < 32; ++j) {
+            const int o0 = __shfl_sync(0xffffffffu, e0, j), o1 = __shfl_sync(0xffffffffu, e1, j);
+            if (e1 >= 0 && o0 == e1) dup_of = j;
+            if (e0 >= 0 && o1 == e0) shared_by_1 = true;
+        }
+        // rows of the first group: 1 or 2 per slot; exclusive scan over lanes
+        const int c0 = e0 >= 0 ? (shared_by_1 ? 2 : 1) : 0;
+        int inc = c0;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += v;
+        }
+        const int row_a = inc - c0;
+        const int total_a = __shfl_sync(0xffffffffu, inc, 31);
+        const bool fresh = e1 >= 0 && dup_of < 0;
+        const unsigned fb = __ballot_sync(0xffffffffu, fresh);
+        const int rank_b = __popc(fb & ((1u << lane) - 1u));
+        const int nfresh = __popc(fb);
+        const int nun = keff0 + nfresh, run = total_a + nfresh;
+        const int row_dup = __shfl_sync(0xffffffffu, row_a, dup_of < 0 ? 0 : dup_of);
+        if (e0 >= 0) {
+            plan.pair_token[row_a] = 0;
+            const ExpertDev ex = experts[e0];
+            GemvSlot g;
+            g.a = ex.gate;
+            g.b = ex.up;
+            g.a_rs = ex.gate_rs;
+            g.b_rs = ex.up_rs;
+            g.row0 = row_a;
+            g.nrows = c0;
+            plan.gu_slots[lane] = g;
+        }
+        if (e1 >= 0) {
+            if (fresh) {
+                plan.pair_token[total_a + rank_b] = 1;
+                const ExpertDev ex = experts[e1];
+                GemvSlot g;
+                g.a = ex.gate;
+                g.b = ex.up;
+                g.a_rs = ex.gate_rs;
+                g.b_rs = ex.up_rs;
+                g.row0 = total_a + rank_b;
+                g.nrows = 1;
+                plan.gu_slots[keff0 + rank_b] = g;
+            } else {
+                plan.pair_token[row_dup + 1] = 1;
+            }
+        }
+        if (has_shared && lane < M) plan.pair_token[run + lane] = lane;
+        if (has_shared && lane == 0) {
+            const ExpertDev ex = experts[E];
+            GemvSlot g;
+            g.a = ex.gate;
+            g.b = ex.up;
+            g.a_rs = ex.gate_rs;
+            g.b_rs = ex.up_rs;
+            g.row0 = run;
+            g.nrows = M;
+            plan.gu_slots[nun] = g;
+        }
+        if (lane == 0) {
+            *plan.n_union = nun;
+            *plan.n_slots = nun + (has_shared ? 1 : 0);
+            *plan.n_pairs = run + (has_shared ? M : 0);
+            *plan.shared_pair0 = has_shared ? run : -1;
+        }
+    }
+}
+
+// Speculative routing launch.  Same outputs as route_fused_kernel (int8 copy of x, logits, plan)
+// but the logits are plain parallel dot products, so they can differ from the reference's
+// sequential fp32 chain in the last bits.  The layer starts the expert launches from this plan
+// while route_fused_kernel computes the exact chains on other SMs; the selections of the two are
+// compared afterwards (see GemvParams::spec_a) and the rare disagreement is recomputed.  Only
+// the *selection* of this plan is ever used: weights and combine order come from the exact plan.
+//   CTAs [0, n_chain_ctas): kSpEPB experts each; the rest: one token each.
+constexpr int kSpEPB = 1, kSpWPE = 8, kSpBatch = 6;
+__global__ void __launch_bounds__(kRtThreads) route_spec_kernel(const RouteArgs A) {
+    extern __shared__ __align__(128) unsigned char rt_smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if ((int)blockIdx.x >= A.n_chain_ctas) {
+        route_quantise_row(A, blockIdx.x - A.n_chain_ctas, rt_smem);
+        return;
+    }
+    // kSpEPB experts per CTA, kSpWPE warps per expert, each warp one contiguous part of D with all
+    // its loads issued before the first use (one memory round trip per kSpBatch float4 per lane)
+    __shared__ float s_part[kSpEPB][kSpWPE][kSpecTokens];
+    const int el = warp / kSpWPE, part = warp % kSpWPE;
+    const int e = blockIdx.x * kSpEPB + el;
+    if (warp < kSpEPB * kSpWPE && e < A.E) {
+        const float4 *wr = reinterpret_cast<const float4 *>(A.rw + (long long)e * A.D);
+        const int n4 = A.D >> 2;
+        const int per = (n4 + kSpWPE - 1) / kSpWPE;
+        const int lo = part * per, hi = min(n4, lo + per);
+        float acc[kSpecTokens];
+#pragma unroll
+        for (int s = 0; s < kSpecTokens; ++s) acc[s] = 0.0f;
+        for (int base = lo; base < hi; base += 32 * kSpBatch) {
+            float4 wv[kSpBatch], xv[kSpecTokens][kSpBatch];
+#pragma unroll
+            for (int u = 0; u < kSpBatch; ++u) {
+                const int i = base + u * 32 + lane;
+                wv[u] = (i < hi) ? __ldg(wr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < kSpecTokens; ++s)
+                    xv[s][u] = (i < hi && s < A.M)
+                                   ? __ldg(reinterpret_cast<const float4 *>(A.x + (long long)s * A.ldx) + i)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < kSpBatch; ++u)
+#pragma unroll
+                for (int s = 0; s < kSpecTokens; ++s)
+                    acc[s] += (xv[s][u].x * wv[u].x + xv[s][u].y * wv[u].y) + (xv[s][u].z * wv[u].z + xv[s][u].w * wv[u].w);
+        }
+#pragma unroll
+        for (int s = 0; s < kSpecTokens; ++s) {
+            float sum = acc[s];
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) s_part[el][part][s] = sum;
+        }
+    }
+    __syncthreads();
+    if (tid < kSpEPB * kSpecTokens) {
+        const int el2 = tid / kSpecTokens, s = tid % kSpecTokens;
+        const int e2 = blockIdx.x * kSpEPB + el2;
+        if (e2 < A.E && s < A.M) {
+            float sum = 0.0f;
+            for (int q = 0; q < kSpWPE; ++q) sum += s_part[el2][q][s];
+            A.logits[(long long)s * A.E + e2] = sum * A.spec_sign;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    __shared__ int s_last;
+    if (tid == 0) {
+        const unsigned old = atomicAdd(A.done_counter, 1u);
+        s_last = (old == (unsigned)A.n_chain_ctas - 1u);
+        if (s_last) *A.done_counter = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    route_plan_small(A.logits, A.bias, A.M, A.E, A.k, A.has_shared, A.experts, A.plan, rt_smem);
 }
 
 // Routing-weighted combine, crates/peregrine-model/src/mlp.rs:111-127 and

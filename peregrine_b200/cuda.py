@@ -21,7 +21,7 @@ from dataclasses import dataclass
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libcoli_cuda_backend.so")
+LIB_PATH = os.environ.get("PEREGRINE_B200_LIB") or os.path.join(_HERE, "libcoli_cuda_backend.so")
 
 # every symbol include/peregrine_b200.h declares
 SYMBOLS = [
@@ -42,7 +42,7 @@ SYMBOLS = [
     # additive entry points
     "coli_cuda_tensor_upload_grouped", "coli_cuda_moe_layer_create", "coli_cuda_moe_layer_set_expert",
     "coli_cuda_moe_layer_free", "coli_cuda_moe_layer_forward_dev", "coli_cuda_moe_layer_forward",
-    "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_last_pairs",
+    "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_set_spec", "coli_cuda_moe_layer_last_pairs",
     "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_moe_layer_ep_partial_dev",
     "coli_cuda_moe_layer_ep_combine_dev", "coli_cuda_moe_layer_set_profile", "coli_cuda_moe_layer_profile",
     "coli_cuda_pipe_gemm_noalloc", "coli_cuda_pipe_embed", "coli_cuda_pipe_argmax", "coli_cuda_last_device_error", "coli_cuda_kernel_launches", "coli_cuda_stream",
@@ -122,6 +122,7 @@ def lib():
         L.coli_cuda_moe_layer_forward.argtypes = [vp, vp, vp, i]
         L.coli_cuda_moe_layer_last_routing.argtypes = [vp, i, vp, vp, vp, vp, vp]
         L.coli_cuda_moe_layer_enable_taps.argtypes = [vp, i]
+        L.coli_cuda_moe_layer_set_spec.argtypes = [vp, i]
         L.coli_cuda_moe_layer_last_pairs.argtypes = [vp, vp, vp, vp, i]
         L.coli_cuda_moe_layer_read_taps.argtypes = [vp, vp, sz, vp, sz]
         L.coli_cuda_moe_layer_set_ep.argtypes = [vp, i, i]
@@ -479,6 +480,11 @@ class MoeLayer:
     def enable_taps(self, on: bool = True):
         lib().coli_cuda_moe_layer_enable_taps(self.handle, int(on))
 
+    def set_spec(self, mode: int):
+        """Speculative routing of decode-sized batches: -1 default, 0 off, 1 on, 2 on with a wrong guess."""
+        if lib().coli_cuda_moe_layer_set_spec(self.handle, int(mode)) != 1:
+            raise CudaError("cuda moe_layer_set_spec failed")
+
     def last_pairs(self, m: int):
         cap = m * (self.k + 1)
         tok = np.zeros(cap, np.int32)
@@ -516,7 +522,10 @@ class MoeLayer:
                                                     first_token, n_tokens) != 1:
             raise CudaError("cuda moe_layer_ep_combine_dev failed")
 
-    STAGES = ("qrow_x_unfused", "route", "route_plan_unfused", "gemv_gateup", "qrow_h_unfused", "gemv_down", "unused")
+    # "join_repair_or_qrow_h": with speculative routing the wait for the exact plan plus the repair
+    # launch; otherwise the separate quantiser of h when the down launch cannot stage it itself
+    STAGES = ("qrow_x_unfused", "route", "route_plan_unfused", "gemv_gateup", "join_repair_or_qrow_h", "gemv_down",
+              "unused")
 
     def set_profile(self, on: bool):
         if lib().coli_cuda_moe_layer_set_profile(self.handle, int(on)) != 1:

@@ -137,3 +137,29 @@ def test_device_pointer_forward_matches_host_forward(dev):
     cuda.lib().coli_cuda_pipe_sync(dev)
     assert np.array_equal(bits(out.cpu().numpy()), bits(want))
     ml.free()
+
+
+@pytest.mark.parametrize("m", [1, 2])
+def test_speculative_routing_modes_agree_bit_for_bit(dev, m):
+    # mode 0: exact chains first; 1: speculative pick checked against the exact chains;
+    # 2: the speculative pick is forced wrong, so the recompute path produces the result
+    layer = synth_layer(300 + m, hidden=512, inter=160, n_experts=40, k=4, gs=32)
+    x = synth_tokens(9 + m, m, 512)
+    want, idx, w, keff, uni = oracle_layer_forward(layer, x, threads=4, want_routing=True)
+    ml = upload_layer(dev, layer)
+    for mode in (0, 1, 2, 1, 0, 2):
+        ml.set_spec(mode)
+        for _ in range(2):
+            got = ml.forward(x)
+            gidx, gw, gkeff, guni = ml.last_routing(m)
+            assert np.array_equal(gidx, idx) and np.array_equal(bits(gw), bits(w)) and list(guni) == list(uni)
+            assert np.array_equal(bits(got), bits(want)), f"mode {mode}"
+    if m == 2:
+        # both tokens equal (every pick of token 1 repeats one of token 0), then partly overlapping picks
+        for xx in (np.repeat(x[:1], 2, axis=0), np.stack([x[0], 0.9 * x[0] + 0.1 * x[1]])):
+            want2 = oracle_layer_forward(layer, xx, threads=4)
+            for mode in (0, 1, 2):
+                ml.set_spec(mode)
+                assert np.array_equal(bits(ml.forward(xx)), bits(want2)), f"mode {mode}"
+    assert cuda.last_device_error(dev) == 0
+    ml.free()
