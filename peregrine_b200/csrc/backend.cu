@@ -12,6 +12,7 @@
 #include "../../include/peregrine_b200.h"
 #include "kernels.cuh"
 #include "kernels_mma.cuh"
+#include "kernels_tile.cuh"
 #include "w4_host.h"
 
 using namespace pgb;
@@ -475,6 +476,32 @@ static bool gemv_can_quant_stage(Ctx *c, int n_xrows, const W4Layout &L, int max
     return max_rows <= 2 && gemv_rows_fit(c, n_xrows, L);
 }
 
+template <bool GROUPED, int BPG>
+static int tile_launch_t(Ctx *c, const GemvParams &P) {
+    auto kfn = ffn_w4a8_tile_kernel<GROUPED, BPG>;
+    static std::atomic<uint32_t> configured{0};
+    const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
+    if (!(configured.load() & bit)) {
+        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemBytes),
+                     "tile kernel shared-memory opt-in"))
+            return 0;
+        configured.fetch_or(bit);
+    }
+    const int n_oblk = (P.mode == 0) ? (P.ntile + 3) / 4 : (P.ntile + 7) / 8;
+    return launch(kfn, dim3(n_oblk, P.tile_rb), dim3(kTileThreads), (size_t)kTileSmemBytes, c->stream,
+                  "w4a8 tile kernel launch", P);
+}
+static int tile_launch(Ctx *c, const GemvParams &P, bool grouped, int bpg) {
+    if (!grouped) return tile_launch_t<false, 1>(c, P);
+    switch (bpg) {
+        case 1: return tile_launch_t<true, 1>(c, P);
+        case 2: return tile_launch_t<true, 2>(c, P);
+        case 4: return tile_launch_t<true, 4>(c, P);
+        case 8: return tile_launch_t<true, 8>(c, P);
+    }
+    return fail("w4a8 tile kernel: unsupported group size");
+}
+
 // Fills the layout-dependent fields and launches.  `max_rows` bounds the rows of any slot:
 // up to 2 rows run the dp4a kernel, more run the tensor-core kernel.
 // `want_quant_stage`: the caller filled x_f32 / amax_bits and wants the kernel to quantise the
@@ -493,6 +520,11 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
     P.cs_stride = L.nblk;
     P.err = c->err_dev;
     const bool grouped = L.grouped != 0;
+    if (P.tile_rb > 0) {
+        if (want_quant_stage) return fail("w4a8 tile kernel: no quantising stage");
+        if (P.pcap <= 0) return fail("w4a8 tile kernel: needs chunk-major activations");
+        return tile_launch(c, P, grouped, L.bpg);
+    }
     if (gemv_uses_mma(max_rows)) {
         if (want_quant_stage) return fail("w4a8 gemv: quantising stage is not available beyond 2 rows per expert");
         if (P.pcap <= 0) return fail("w4a8 gemv: the tensor-core kernel needs chunk-major activations");

@@ -200,6 +200,7 @@ struct GemvParams {
     int spec_n, spec_m;
     const unsigned *amax_alt;
     int grid;  // host only: CTAs to launch (0 = one per SM)
+    int tile_rb;  // host only: > 0 selects the large-batch tile kernel with this many row blocks in the grid
     const int *n_xrows_dev;     // rows actually valid (device scalar; nullptr: n_xrows)
     unsigned *amax_out;   // mode 0: per pair row, atomicMax of |h| bits (nullptr: off)
     float *out;
@@ -767,7 +768,8 @@ __host__ __device__ inline size_t route_plan_smem_bytes(int E, int nwarp, int k)
 __device__ __forceinline__ void route_plan_body(const float *__restrict__ logits, const float *__restrict__ bias,
                                                 int M, int E, int k, int norm_topk, float routed_scale,
                                                 int has_shared, const ExpertDev *__restrict__ experts,
-                                                const RoutePlan &plan, unsigned char *rp_smem) {
+                                                const RoutePlan &plan, unsigned char *rp_smem,
+                                                bool preselected = false) {
     const int nwarp = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float *sig_all = reinterpret_cast<float *>(rp_smem);
@@ -783,7 +785,7 @@ __device__ __forceinline__ void route_plan_body(const float *__restrict__ logits
     int *idx_c = s_nunion + 8;                                // kPlanCacheTokens * k
     float *w_c = reinterpret_cast<float *>(idx_c + kPlanCacheTokens * k);
     int *keff_c = reinterpret_cast<int *>(w_c + kPlanCacheTokens * k);
-    const bool cached = M <= kPlanCacheTokens;
+    const bool cached = M <= kPlanCacheTokens && !preselected;
     auto ld_idx = [&](int q) { return cached ? idx_c[q] : plan.idx[q]; };
     auto ld_w = [&](int q) { return cached ? w_c[q] : plan.w[q]; };
     auto ld_keff = [&](int s) { return cached ? keff_c[s] : plan.keff[s]; };
@@ -797,7 +799,9 @@ __device__ __forceinline__ void route_plan_body(const float *__restrict__ logits
     // for token g0 + w.  A score is turned into an order-preserving 32-bit key (0 = not
     // selectable: NaN or -inf, which strict '>' from -inf never picks) so that a round is one
     // warp-wide integer max plus one integer min for the lowest index among equals.
-    for (int g0 = 0; g0 < M; g0 += nwarp) {
+    // (preselected: route_select_kernel already wrote idx / w / keff of every token; only for
+    // batches too large for the shared-memory mirror)
+    for (int g0 = 0; g0 < (preselected ? 0 : M); g0 += nwarp) {
         const int ng = min(nwarp, M - g0);
         for (int i = threadIdx.x; i < ng * E; i += blockDim.x) {
             const int sl = i / E, e = i - sl * E;
@@ -1022,9 +1026,73 @@ __device__ __forceinline__ void route_plan_body(const float *__restrict__ logits
 __global__ void __launch_bounds__(256) route_plan_kernel(const float *__restrict__ logits,
                                                          const float *__restrict__ bias, int M, int E, int k,
                                                          int norm_topk, float routed_scale, int has_shared,
-                                                         const ExpertDev *__restrict__ experts, RoutePlan plan) {
+                                                         const ExpertDev *__restrict__ experts, RoutePlan plan,
+                                                         int preselected) {
     extern __shared__ __align__(16) unsigned char rp_smem[];
-    route_plan_body(logits, bias, M, E, k, norm_topk, routed_scale, has_shared, experts, plan, rp_smem);
+    route_plan_body(logits, bias, M, E, k, norm_topk, routed_scale, has_shared, experts, plan, rp_smem,
+                    preselected != 0);
+}
+
+// Per-token selection for large batches: one warp per token, any number of CTAs.  Same rules and
+// the same arithmetic as step 1 of route_plan_body (crates/peregrine-model/src/router.rs:86-150).
+__global__ void __launch_bounds__(256) route_select_kernel(const float *__restrict__ logits,
+                                                           const float *__restrict__ bias, int M, int E, int k,
+                                                           int norm_topk, float routed_scale, RoutePlan plan) {
+    extern __shared__ __align__(16) unsigned char rs_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    const int s = blockIdx.x * nwarp + warp;
+    if (s >= M) return;
+    float *sig = reinterpret_cast<float *>(rs_smem) + warp * 2 * E;
+    unsigned *key = reinterpret_cast<unsigned *>(sig + E);
+    for (int e = lane; e < E; e += 32) {
+        const float sg = sigmoid32(__ldcg(logits + (long long)s * E + e));
+        sig[e] = sg;
+        const float c = __fadd_rn(sg, bias[e]);
+        unsigned u = 0u;
+        if (c > -INFINITY) {  // false for NaN and -inf
+            u = __float_as_uint(c == 0.0f ? 0.0f : c);
+            u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        }
+        key[e] = u;
+    }
+    __syncwarp();
+    int kept = k, my_idx = 0;
+    float my_w = 0.0f;
+    for (int kk = 0; kk < k; ++kk) {
+        unsigned bu = 0u;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const unsigned u = key[e];
+            if (u > bu) {
+                bu = u;
+                bi = e;
+            }
+        }
+        const unsigned top = __reduce_max_sync(0xffffffffu, bu);
+        if (top == 0u) {
+            kept = kk;
+            break;
+        }
+        const int best = (int)__reduce_min_sync(0xffffffffu, (unsigned)(bu == top ? bi : 0x7fffffff));
+        if (lane == kk) {
+            my_idx = best;
+            my_w = sig[best];
+        }
+        if (lane == 0) key[best] = 0u;
+        __syncwarp();
+    }
+    if (norm_topk) {
+        float sm = 0.0f;
+        for (int j = 0; j < k; ++j) sm = __fadd_rn(sm, __shfl_sync(0xffffffffu, my_w, j));
+        sm = __fadd_rn(sm, 1e-20f);
+        my_w = __fdiv_rn(my_w, sm);
+    }
+    my_w = __fmul_rn(my_w, routed_scale);
+    if (lane < k) {
+        plan.idx[s * k + lane] = my_idx;
+        plan.w[s * k + lane] = my_w;
+    }
+    if (lane == 0) plan.keff[s] = kept;
 }
 
 // ------------------------------------------------- fused routing kernel
@@ -1070,6 +1138,7 @@ struct RouteArgs {
     int *xcs;
     int kp, nblk;
     int *err;
+    int no_plan;      // route_fused_kernel: logits and quantised rows only (large batches plan separately)
     float spec_sign;  // route_spec_kernel: -1 turns the speculative pick upside down (repair-path self-test)
 };
 
@@ -1383,7 +1452,7 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
         if (*s_last) *A.done_counter = 0u;
     }
     __syncthreads();
-    if (!*s_last) return;
+    if (!*s_last || A.no_plan) return;
     __threadfence();
     route_plan_body(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts, A.plan,
                     rt_smem);
