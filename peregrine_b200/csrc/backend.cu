@@ -13,6 +13,7 @@
 #include "kernels.cuh"
 #include "kernels_mma.cuh"
 #include "kernels_tile.cuh"
+#include "kernels_umma.cuh"
 #include "w4_host.h"
 
 using namespace pgb;
@@ -491,7 +492,32 @@ static int tile_launch_t(Ctx *c, const GemvParams &P) {
     return launch(kfn, dim3(n_oblk, P.tile_rb), dim3(kTileThreads), (size_t)kTileSmemBytes, c->stream,
                   "w4a8 tile kernel launch", P);
 }
+template <bool GROUPED, int BPG>
+static int umma_launch_t(Ctx *c, const GemvParams &P) {
+    auto kfn = ffn_w4a8_umma_kernel<GROUPED, BPG>;
+    static std::atomic<uint32_t> configured{0};
+    const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
+    if (!(configured.load() & bit)) {
+        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kUmSmemBytes),
+                     "tcgen05 kernel shared-memory opt-in"))
+            return 0;
+        configured.fetch_or(bit);
+    }
+    const int n_oblk = (P.mode == 0) ? (P.ntile + 3) / 4 : (P.ntile + 7) / 8;
+    return launch(kfn, dim3(n_oblk, P.tile_rb), dim3(kUmThreads), (size_t)kUmSmemBytes, c->stream,
+                  "w4a8 tcgen05 kernel launch", P);
+}
 static int tile_launch(Ctx *c, const GemvParams &P, bool grouped, int bpg) {
+    if (P.umma) {
+        if (!grouped) return umma_launch_t<false, 1>(c, P);
+        switch (bpg) {
+            case 1: return umma_launch_t<true, 1>(c, P);
+            case 2: return umma_launch_t<true, 2>(c, P);
+            case 4: return umma_launch_t<true, 4>(c, P);
+            case 8: return umma_launch_t<true, 8>(c, P);
+        }
+        return fail("w4a8 tcgen05 kernel: unsupported group size");
+    }
     if (!grouped) return tile_launch_t<false, 1>(c, P);
     switch (bpg) {
         case 1: return tile_launch_t<true, 1>(c, P);

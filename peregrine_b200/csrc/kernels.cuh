@@ -74,7 +74,8 @@ constexpr int kXqChunkRowBytes = kChunkElems + 16;
 // int8 row (zero padded) and its scale it writes, per 32-element block,
 // -8 * sum(q): the term that turns the stream's stored nibbles (v+8) back into
 // signed weights inside the integer dot.  `rowmap` (optional) names the source row
-// of output row r; `pcap` > 0 selects the chunk-major layout with that row capacity.
+// of output row r; `pcap` > 0 selects the chunk-major layout with that row capacity, `pcap` < 0
+// the core-matrix layout of the tcgen05 kernel with capacity -pcap.
 __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ x, long long ldx, int K, int kp,
                                                       int nblk, int8_t *__restrict__ xq, float *__restrict__ sx,
                                                       int *__restrict__ csum, const int *__restrict__ n_rows_dev,
@@ -117,7 +118,13 @@ __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ 
         }
         int sum = q;
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (pcap > 0) {
+        if (pcap < 0) {
+            // core-matrix order for the tcgen05 kernel: [chunk][16-element unit][row][16 bytes]
+            const long long cap = -pcap;
+            const int kk = (blk & 7) * 32 + lane;
+            xq[((((long long)(blk >> 3) * 16 + (kk >> 4)) * cap + row) << 4) + (kk & 15)] = (int8_t)q;
+            if (lane == 0) csum[((long long)(blk >> 3) * cap + row) * kChunkBlocks + (blk & 7)] = -8 * sum;
+        } else if (pcap > 0) {
             const long long cr = (long long)(blk >> 3) * pcap + row;
             xq[cr * kXqChunkRowBytes + (blk & 7) * 32 + lane] = (int8_t)q;
             if (lane == 0) csum[cr * kChunkBlocks + (blk & 7)] = -8 * sum;
@@ -201,6 +208,7 @@ struct GemvParams {
     const unsigned *amax_alt;
     int grid;  // host only: CTAs to launch (0 = one per SM)
     int tile_rb;  // host only: > 0 selects the large-batch tile kernel with this many row blocks in the grid
+    int umma;     // host only: with tile_rb > 0, take the tcgen05 kernel (activations in core-matrix order)
     const int *n_xrows_dev;     // rows actually valid (device scalar; nullptr: n_xrows)
     unsigned *amax_out;   // mode 0: per pair row, atomicMax of |h| bits (nullptr: off)
     float *out;

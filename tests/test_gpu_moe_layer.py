@@ -165,12 +165,13 @@ def test_speculative_routing_modes_agree_bit_for_bit(dev, m):
     ml.free()
 
 
-@pytest.mark.parametrize("gs,hidden,inter,m", [(32, 512, 160, 200), (128, 384, 256, 150), (0, 256, 96, 140),
+@pytest.mark.parametrize("kernel", ["1", "2"])  # 1: mma.sync tiles, 2: tcgen05 tiles
+@pytest.mark.parametrize("gs,hidden,inter,m", [(0, 256, 96, 140), (32, 512, 160, 200), (128, 384, 256, 150),
                                                (64, 512, 128, 37)])
-def test_large_batch_tile_kernel_matches_oracle_bit_for_bit(dev, monkeypatch, gs, hidden, inter, m):
-    # the CTA-tiled kernel forced on: several 128-row blocks per expert, ragged last blocks,
+def test_large_batch_tile_kernel_matches_oracle_bit_for_bit(dev, monkeypatch, gs, hidden, inter, m, kernel):
+    # the CTA-tiled kernels forced on: several 128-row blocks per expert, ragged last blocks,
     # weight-row blocks that run past the matrix (inter not a multiple of 64)
-    monkeypatch.setenv("PEREGRINE_B200_TILE", "1")
+    monkeypatch.setenv("PEREGRINE_B200_TILE", kernel)
     layer = synth_layer(400 + m, hidden=hidden, inter=inter, n_experts=6, k=2, gs=gs)
     x = synth_tokens(70 + m, m, hidden)
     got = check_layer(dev, layer, x)
