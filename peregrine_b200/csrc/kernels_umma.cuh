@@ -88,10 +88,25 @@ __device__ __forceinline__ void tmem_fill32(uint32_t taddr, int v) {
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// try_wait that lets the hardware park the thread for up to `ns` nanoseconds instead of
+// returning at once: the waiting roles of this kernel share their schedulers with the fold warps
+// and must not spend issue slots on polling
+__device__ __forceinline__ uint32_t mbar_try_wait_park(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok;
+}
+
 // bounded wait that also gives up when another role has already failed
 __device__ __forceinline__ bool um_wait(uint32_t bar, uint32_t parity, volatile int *fail) {
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_park(bar, parity, 20000u)) {
         if (*fail) return false;
         if (clock64() - t0 > 2000000000LL) {
             *fail = 1;
