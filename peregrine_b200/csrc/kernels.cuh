@@ -42,6 +42,7 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
@@ -364,7 +365,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
         const int q4_per_row = P.xq_stride >> 2;
         const int total4 = nrows_valid * q4_per_row;
         const bool vec_ok = ((P.x_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(P.x_f32) & 15) == 0);
-        constexpr int kBatch = 4;
+        constexpr int kBatch = 12;  // a decode step's 9 rows of 2048 are one batch: a single round trip to L2
         for (int base4 = 0; base4 < total4; base4 += kBatch * kGemvThreads) {
             float4 v[kBatch];
             int rowv[kBatch], c4v[kBatch];
@@ -1298,7 +1299,12 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
         // wait at the CTA barrier below without issuing, so nothing competes with the chain.
         const uint32_t prod_u32 = empty_u32 + kRtMaxStages * 8;  // [stage] products ready
         if (warp >= 4) {
-            // nothing to do until the plan
+            // nothing to do until the plan, except warming what the plan will read
+            if (warp == 4 && lane < ne) {
+                prefetch_l2(A.bias + e0 + lane);
+                prefetch_l2(A.experts + e0 + lane);
+                if (blockIdx.x == 0 && lane == 0) prefetch_l2(A.experts + A.E);
+            }
         } else if (warp == 1 || warp == 3) {
             for (int i = 0; i < nslice; ++i) {
                 const int st = i % kRtStages;
@@ -1633,6 +1639,13 @@ __global__ void __launch_bounds__(kRtThreads) route_spec_kernel(const RouteArgs 
     __shared__ float s_part[kSpEPB][kSpWPE][kSpecTokens];
     const int el = warp / kSpWPE, part = warp % kSpWPE;
     const int e = blockIdx.x * kSpEPB + el;
+    // the planning CTA reads bias and expert-table entries in a dependent chain at the very end of
+    // this launch: pull them into L2 now (after an L2-cold start each would be a DRAM round trip)
+    if (tid == 0 && e < A.E) {
+        prefetch_l2(A.bias + e);
+        prefetch_l2(A.experts + e);
+        if (blockIdx.x == 0) prefetch_l2(A.experts + A.E);
+    }
     if (warp < kSpEPB * kSpWPE && e < A.E) {
         const float4 *wr = reinterpret_cast<const float4 *>(A.rw + (long long)e * A.D);
         const int n4 = A.D >> 2;
