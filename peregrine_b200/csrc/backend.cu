@@ -112,6 +112,25 @@ static int reserve(Ctx *c, DevBuf &b, size_t bytes, bool pinned = false) {
     return 1;
 }
 
+// Launch that may begin while the previous launch of the stream is still running (programmatic
+// dependent launch); the kernel orders itself with griddepcontrol.wait.
+template <typename... KArgs, typename... Args>
+static int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      const char *what, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_ok(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...), what);
+}
+
 template <typename... KArgs, typename... Args>
 static int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const char *what,
                   Args... args) {
@@ -400,6 +419,9 @@ static int gemv_launch_t(Ctx *c, const GemvParams &P, size_t smem) {
             return 0;
         configured.fetch_or(bit);
     }
+    if (P.pdl)
+        return launch_pdl(kfn, dim3(P.grid > 0 ? P.grid : c->sms), dim3(kGemvThreads), smem, c->stream,
+                          "w4a8 gemv launch", P);
     return launch(kfn, dim3(P.grid > 0 ? P.grid : c->sms), dim3(kGemvThreads), smem, c->stream, "w4a8 gemv launch", P);
 }
 

@@ -42,6 +42,11 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// Programmatic dependent launch: a launch made with the programmatic-serialisation attribute may
+// start while its predecessor in the stream is still running; it must not touch anything the
+// predecessor writes before griddep_wait().  Both are no-ops in an ordinary launch.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -208,6 +213,7 @@ struct GemvParams {
     int spec_n, spec_m;
     const unsigned *amax_alt;
     int grid;  // host only: CTAs to launch (0 = one per SM)
+    int pdl;   // host only: launch with programmatic stream serialisation (see griddep_wait)
     int tile_rb;  // host only: > 0 selects the large-batch tile kernel with this many row blocks in the grid
     int umma;     // host only: with tile_rb > 0, take the tcgen05 kernel (activations in core-matrix order)
     const int *n_xrows_dev;     // rows actually valid (device scalar; nullptr: n_xrows)
@@ -287,6 +293,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = lane >> 4, r16 = lane & 15;
+    // gate/up reads its slot table from the launch before it; a down launch only depends on its
+    // predecessor (the repair launch) for the activation rows, see below
+    griddep_launch_dependents();
+    if (P.mode == 0) griddep_wait();
     bool spec_same = true;
     if (P.spec_a) {
         int bad = 0;
@@ -339,6 +349,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
         ++fq;
     }
 
+    // everything above (plan, weight prefetch) is independent of the preceding launch; the
+    // activation rows and their row maxima are not
+    if (P.mode != 0) griddep_wait();
     if (XS == 1) {
         const int n16 = xs_bytes >> 4;
         const uint4 *src = reinterpret_cast<const uint4 *>(P.xq);
@@ -1630,6 +1643,7 @@ constexpr int kSpEPB = 1, kSpWPE = 8, kSpBatch = 6;
 __global__ void __launch_bounds__(kRtThreads) route_spec_kernel(const RouteArgs A) {
     extern __shared__ __align__(128) unsigned char rt_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    griddep_launch_dependents();
     if ((int)blockIdx.x >= A.n_chain_ctas) {
         route_quantise_row(A, blockIdx.x - A.n_chain_ctas, rt_smem);
         return;
