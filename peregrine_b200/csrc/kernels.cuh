@@ -1160,9 +1160,203 @@ struct RouteArgs {
     int *xcs;
     int kp, nblk;
     int *err;
+    int small_plan;   // route_fused_kernel: at most kSpecTokens tokens on one device: route_plan_small<true>
     int no_plan;      // route_fused_kernel: logits and quantised rows only (large batches plan separately)
     float spec_sign;  // route_spec_kernel: -1 turns the speculative pick upside down (repair-path self-test)
 };
+
+// Plan for at most kSpecTokens tokens on one device, two uses:
+//   EXACT = false: plan of a speculative selection.  Only what the gate/up launch reads is produced
+//     (selection ids, pair rows, gate/up slots, cleared scratch), with the numbering rules of
+//     route_plan_body, so that an agreeing exact plan describes the same rows.  Scores use the fast
+//     fp32 exponential: a guess does not need more.
+//   EXACT = true: the complete plan with the arithmetic of route_plan_body step 1
+//     (crates/peregrine-model/src/router.rs:86-150) and the same layout rules, written for one or
+//     two tokens so that no phase is longer than a warp's worth of work: it runs at the end of the
+//     exact chains, which the down launch of a decode step waits for.
+constexpr int kSpecTokens = 2;
+template <bool EXACT>
+__device__ __forceinline__ void route_plan_small(const float *__restrict__ logits, const float *__restrict__ bias,
+                                                 int M, int E, int k, int norm_topk, float routed_scale,
+                                                 int has_shared, const ExpertDev *__restrict__ experts,
+                                                 const RoutePlan &plan, unsigned char *rp_smem) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned *key_all = reinterpret_cast<unsigned *>(rp_smem);        // [kSpecTokens][E]
+    int *idx_s = reinterpret_cast<int *>(key_all + kSpecTokens * E);  // [kSpecTokens][32]
+    int *keff_s = idx_s + kSpecTokens * 32;                           // [kSpecTokens]
+    float *w_s = reinterpret_cast<float *>(keff_s + kSpecTokens);     // [kSpecTokens][32]
+    float *sig_all = w_s + kSpecTokens * 32;                          // [kSpecTokens][E] (EXACT)
+    for (int i = threadIdx.x; i < plan.n_col; i += blockDim.x) plan.col_done[i] = 0;
+    for (int i = threadIdx.x; i < plan.n_amax; i += blockDim.x) plan.amax[i] = 0u;
+    if (warp < M) {
+        const int s = warp;
+        unsigned *key = key_all + s * E;
+        float *sig = sig_all + s * E;
+        // scores: eight experts per lane and round trip to memory
+        for (int e0 = 0; e0 < E; e0 += 256) {
+            float lg[8], bs[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = e0 + u * 32 + lane;
+                lg[u] = e < E ? __ldcg(logits + (long long)s * E + e) : 0.0f;
+                bs[u] = e < E ? __ldg(bias + e) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = e0 + u * 32 + lane;
+                float c;
+                if (EXACT) {
+                    const float sg = sigmoid32(lg[u]);
+                    if (e < E) sig[e] = sg;
+                    c = __fadd_rn(sg, bs[u]);
+                } else {
+                    c = __fdividef(1.0f, 1.0f + __expf(-lg[u])) + bs[u];
+                }
+                unsigned q = 0u;
+                if (c > -INFINITY) {  // false for NaN and -inf: never selectable
+                    q = __float_as_uint(c == 0.0f ? 0.0f : c);
+                    q = (q & 0x80000000u) ? ~q : (q | 0x80000000u);
+                }
+                if (e < E) key[e] = q;
+            }
+        }
+        __syncwarp();
+        int kept = k;
+        int my_idx = 0;
+        float my_w = 0.0f;
+        for (int kk = 0; kk < k; ++kk) {
+            unsigned bu = 0u;
+            int bi = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const unsigned u = key[e];
+                if (u > bu) {  // ascending e within a lane: the first maximum keeps the lowest index
+                    bu = u;
+                    bi = e;
+                }
+            }
+            const unsigned top = __reduce_max_sync(0xffffffffu, bu);
+            if (top == 0u) {
+                kept = kk;
+                break;
+            }
+            const int best = (int)__reduce_min_sync(0xffffffffu, (unsigned)(bu == top ? bi : 0x7fffffff));
+            if (lane == kk) {
+                my_idx = best;
+                if (EXACT) my_w = sig[best];
+            }
+            if (lane == 0) key[best] = 0u;
+            __syncwarp();
+        }
+        if (EXACT) {
+            // slots >= kept hold expert 0 with weight 0 (the initial values)
+            if (norm_topk) {
+                float sm = 0.0f;
+                for (int j = 0; j < k; ++j) sm = __fadd_rn(sm, __shfl_sync(0xffffffffu, my_w, j));
+                sm = __fadd_rn(sm, 1e-20f);
+                my_w = __fdiv_rn(my_w, sm);
+            }
+            my_w = __fmul_rn(my_w, routed_scale);
+        }
+        idx_s[s * 32 + lane] = my_idx;
+        w_s[s * 32 + lane] = my_w;
+        if (lane < k) {
+            plan.idx[s * k + lane] = my_idx;
+            if (EXACT) plan.w[s * k + lane] = my_w;
+        }
+        if (lane == 0) {
+            keff_s[s] = kept;
+            plan.keff[s] = kept;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // Union and pair rows for one or two tokens, lane kk = selection kk.  Token 0's picks are
+        // union slots 0..keff0-1 in order; a pick of token 1 either repeats one of them (its row
+        // follows token 0's row of that expert) or opens a new slot in kk order.
+        const int keff0 = keff_s[0], keff1 = M > 1 ? keff_s[1] : 0;
+        const int e0 = lane < keff0 ? idx_s[lane] : -1;
+        const int e1 = lane < keff1 ? idx_s[32 + lane] : -2;
+        int dup_of = -1;           // slot of token 0 that my token-1 pick repeats
+        bool shared_by_1 = false;  // my token-0 pick is repeated by token 1
+        for (int j = 0; j < 32; ++j) {
+            const int o0 = __shfl_sync(0xffffffffu, e0, j), o1 = __shfl_sync(0xffffffffu, e1, j);
+            if (e1 >= 0 && o0 == e1) dup_of = j;
+            if (e0 >= 0 && o1 == e0) shared_by_1 = true;
+        }
+        // rows of the first group: 1 or 2 per slot; exclusive scan over lanes
+        const int c0 = e0 >= 0 ? (shared_by_1 ? 2 : 1) : 0;
+        int inc = c0;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += v;
+        }
+        const int row_a = inc - c0;
+        const int total_a = __shfl_sync(0xffffffffu, inc, 31);
+        const bool fresh = e1 >= 0 && dup_of < 0;
+        const unsigned fb = __ballot_sync(0xffffffffu, fresh);
+        const int rank_b = __popc(fb & ((1u << lane) - 1u));
+        const int nfresh = __popc(fb);
+        const int nun = keff0 + nfresh, run = total_a + nfresh;
+        const int row_dup = __shfl_sync(0xffffffffu, row_a, dup_of < 0 ? 0 : dup_of);
+        auto slot_of = [&](int e_id, int r0, int n, int p) {
+            const ExpertDev ex = experts[e_id];
+            GemvSlot g;
+            g.a = ex.gate;
+            g.b = ex.up;
+            g.a_rs = ex.gate_rs;
+            g.b_rs = ex.up_rs;
+            g.row0 = r0;
+            g.nrows = n;
+            plan.gu_slots[p] = g;
+            if (EXACT) {
+                g.a = ex.down;
+                g.b = nullptr;
+                g.a_rs = ex.down_rs;
+                g.b_rs = nullptr;
+                plan.dn_slots[p] = g;
+            }
+        };
+        if (e0 >= 0) {
+            plan.pair_token[row_a] = 0;
+            slot_of(e0, row_a, c0, lane);
+            if (EXACT) {
+                plan.union_ids[lane] = e0;
+                plan.tok_pair[lane] = row_a;
+                plan.comb_pair[lane] = row_a;  // a single token's union order is its selection order
+                plan.comb_w[lane] = w_s[lane];
+            }
+        }
+        // token 1: union position and pair row of my pick
+        const int slot1 = e1 >= 0 ? (fresh ? keff0 + rank_b : dup_of) : 0x7fffffff;
+        const int row1 = fresh ? total_a + rank_b : row_dup + 1;
+        if (e1 >= 0) {
+            plan.pair_token[row1] = 1;
+            if (fresh) slot_of(e1, row1, 1, keff0 + rank_b);
+        }
+        if (EXACT && M > 1) {
+            // combine order of token 1: its picks by ascending union position
+            int pos = 0;
+            for (int j = 0; j < 32; ++j) {
+                const int other = __shfl_sync(0xffffffffu, slot1, j);
+                pos += (other < slot1) ? 1 : 0;
+            }
+            if (e1 >= 0) {
+                if (fresh) plan.union_ids[keff0 + rank_b] = e1;
+                plan.tok_pair[k + lane] = row1;
+                plan.comb_pair[k + pos] = row1;
+                plan.comb_w[k + pos] = w_s[32 + lane];
+            }
+        }
+        if (has_shared && lane < M) plan.pair_token[run + lane] = lane;
+        if (has_shared && lane == 0) slot_of(E, run, M, nun);
+        if (lane == 0) {
+            *plan.n_union = nun;
+            *plan.n_slots = nun + (has_shared ? 1 : 0);
+            *plan.n_pairs = run + (has_shared ? M : 0);
+            *plan.shared_pair0 = has_shared ? run : -1;
+        }
+    }
+}
 
 // Quantiser role of the routing launches (crates/peregrine-kernels/src/quant.rs:14-33): one CTA
 // turns token `row` into int8 with its scale and the -8*sum correction of every 32-block.
@@ -1481,155 +1675,12 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
     __syncthreads();
     if (!*s_last || A.no_plan) return;
     __threadfence();
-    route_plan_body(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts, A.plan,
-                    rt_smem);
-}
-
-// Plan of a speculative selection for at most kSpecTokens tokens on one device.  Only what the
-// gate/up launch reads is produced (selection ids, pair rows, gate/up slots, cleared scratch) with
-// the numbering rules of route_plan_body, so that an agreeing exact plan describes the same rows.
-constexpr int kSpecTokens = 2;
-__device__ __forceinline__ void route_plan_small(const float *__restrict__ logits, const float *__restrict__ bias,
-                                                 int M, int E, int k, int has_shared,
-                                                 const ExpertDev *__restrict__ experts, const RoutePlan &plan,
-                                                 unsigned char *rp_smem) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    unsigned *key_all = reinterpret_cast<unsigned *>(rp_smem);        // [kSpecTokens][E]
-    int *idx_s = reinterpret_cast<int *>(key_all + kSpecTokens * E);  // [kSpecTokens][32]
-    int *keff_s = idx_s + kSpecTokens * 32;                           // [kSpecTokens]
-    for (int i = threadIdx.x; i < plan.n_col; i += blockDim.x) plan.col_done[i] = 0;
-    for (int i = threadIdx.x; i < plan.n_amax; i += blockDim.x) plan.amax[i] = 0u;
-    if (warp < M) {
-        const int s = warp;
-        unsigned *key = key_all + s * E;
-        // scores: eight experts per lane and round trip; the fast exponential is enough for a guess
-        for (int e0 = 0; e0 < E; e0 += 256) {
-            float lg[8], bs[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int e = e0 + u * 32 + lane;
-                lg[u] = e < E ? __ldcg(logits + (long long)s * E + e) : 0.0f;
-                bs[u] = e < E ? __ldg(bias + e) : 0.0f;
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int e = e0 + u * 32 + lane;
-                const float c = __fdividef(1.0f, 1.0f + __expf(-lg[u])) + bs[u];
-                unsigned q = 0u;
-                if (c > -INFINITY) {
-                    q = __float_as_uint(c == 0.0f ? 0.0f : c);
-                    q = (q & 0x80000000u) ? ~q : (q | 0x80000000u);
-                }
-                if (e < E) key[e] = q;
-            }
-        }
-        __syncwarp();
-        int kept = k;
-        for (int kk = 0; kk < k; ++kk) {
-            unsigned bu = 0u;
-            int bi = 0x7fffffff;
-            for (int e = lane; e < E; e += 32) {
-                const unsigned u = key[e];
-                if (u > bu) {
-                    bu = u;
-                    bi = e;
-                }
-            }
-            const unsigned top = __reduce_max_sync(0xffffffffu, bu);
-            if (top == 0u) {
-                kept = kk;
-                break;
-            }
-            const int best = (int)__reduce_min_sync(0xffffffffu, (unsigned)(bu == top ? bi : 0x7fffffff));
-            if (lane == 0) {
-                key[best] = 0u;
-                idx_s[s * 32 + kk] = best;
-            }
-            __syncwarp();
-        }
-        if (lane < k) plan.idx[s * k + lane] = lane < kept ? idx_s[s * 32 + lane] : 0;
-        if (lane == 0) {
-            keff_s[s] = kept;
-            plan.keff[s] = kept;
-        }
-    }
-    __syncthreads();
-    if (warp == 0) {
-        // Union and pair rows for one or two tokens, lane kk = selection kk.  Token 0's picks are
-        // union slots 0..keff0-1 in order; a pick of token 1 either repeats one of them (its row
-        // follows token 0's row of that expert) or opens a new slot in kk order.
-        const int keff0 = keff_s[0], keff1 = M > 1 ? keff_s[1] : 0;
-        const int e0 = lane < keff0 ? idx_s[lane] : -1;
-        const int e1 = lane < keff1 ? idx_s[32 + lane] : -2;
-        int dup_of = -1;      // slot of token 0 that my token-1 pick repeats
-        bool shared_by_1 = false;  // my token-0 pick is repeated by token 1
-        for (int j = 0; j < 32; ++j) {
-            const int o0 = __shfl_sync(0xffffffffu, e0, j), o1 = __shfl_sync(0xffffffffu, e1, j);
-            if (e1 >= 0 && o0 == e1) dup_of = j;
-            if (e0 >= 0 && o1 == e0) shared_by_1 = true;
-        }
-        // rows of the first group: 1 or 2 per slot; exclusive scan over lanes
-        const int c0 = e0 >= 0 ? (shared_by_1 ? 2 : 1) : 0;
-        int inc = c0;
-        for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, inc, o);
-            if (lane >= o) inc += v;
-        }
-        const int row_a = inc - c0;
-        const int total_a = __shfl_sync(0xffffffffu, inc, 31);
-        const bool fresh = e1 >= 0 && dup_of < 0;
-        const unsigned fb = __ballot_sync(0xffffffffu, fresh);
-        const int rank_b = __popc(fb & ((1u << lane) - 1u));
-        const int nfresh = __popc(fb);
-        const int nun = keff0 + nfresh, run = total_a + nfresh;
-        const int row_dup = __shfl_sync(0xffffffffu, row_a, dup_of < 0 ? 0 : dup_of);
-        if (e0 >= 0) {
-            plan.pair_token[row_a] = 0;
-            const ExpertDev ex = experts[e0];
-            GemvSlot g;
-            g.a = ex.gate;
-            g.b = ex.up;
-            g.a_rs = ex.gate_rs;
-            g.b_rs = ex.up_rs;
-            g.row0 = row_a;
-            g.nrows = c0;
-            plan.gu_slots[lane] = g;
-        }
-        if (e1 >= 0) {
-            if (fresh) {
-                plan.pair_token[total_a + rank_b] = 1;
-                const ExpertDev ex = experts[e1];
-                GemvSlot g;
-                g.a = ex.gate;
-                g.b = ex.up;
-                g.a_rs = ex.gate_rs;
-                g.b_rs = ex.up_rs;
-                g.row0 = total_a + rank_b;
-                g.nrows = 1;
-                plan.gu_slots[keff0 + rank_b] = g;
-            } else {
-                plan.pair_token[row_dup + 1] = 1;
-            }
-        }
-        if (has_shared && lane < M) plan.pair_token[run + lane] = lane;
-        if (has_shared && lane == 0) {
-            const ExpertDev ex = experts[E];
-            GemvSlot g;
-            g.a = ex.gate;
-            g.b = ex.up;
-            g.a_rs = ex.gate_rs;
-            g.b_rs = ex.up_rs;
-            g.row0 = run;
-            g.nrows = M;
-            plan.gu_slots[nun] = g;
-        }
-        if (lane == 0) {
-            *plan.n_union = nun;
-            *plan.n_slots = nun + (has_shared ? 1 : 0);
-            *plan.n_pairs = run + (has_shared ? M : 0);
-            *plan.shared_pair0 = has_shared ? run : -1;
-        }
-    }
+    if (A.small_plan)
+        route_plan_small<true>(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts,
+                               A.plan, rt_smem);
+    else
+        route_plan_body(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts, A.plan,
+                        rt_smem);
 }
 
 // Speculative routing launch.  Same outputs as route_fused_kernel (int8 copy of x, logits, plan)
@@ -1714,7 +1765,8 @@ __global__ void __launch_bounds__(kRtThreads) route_spec_kernel(const RouteArgs 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    route_plan_small(A.logits, A.bias, A.M, A.E, A.k, A.has_shared, A.experts, A.plan, rt_smem);
+    route_plan_small<false>(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts,
+                            A.plan, rt_smem);
 }
 
 // Routing-weighted combine, crates/peregrine-model/src/mlp.rs:111-127 and
