@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the MoE expert-FFN decode path (BASELINE.json configs[1]).
+"""Benchmark of the MoE expert-FFN decode path (the headline config: one decode layer).
 
 One "step" is one decode pass of one MoE layer over M tokens (default M = 1):
 router -> top-k -> batch union -> int4 x int8 gate/up + SwiGLU -> down ->
@@ -27,7 +27,7 @@ if ROOT not in sys.path:
 
 import numpy as np  # noqa: E402
 
-# BASELINE.json configs[1]: single decode layer, all experts resident
+# headline config: single decode layer, all experts resident
 CFG = dict(hidden=6144, inter=2048, n_experts=256, k=8, n_shared=1, gs=32, norm_topk=True, routed_scale=2.5)
 METRIC = "moe_expert_ffn_decode_tok_s"
 UNIT = "tok/s"

@@ -1,4 +1,4 @@
-"""Synthetic FFN-only decode stack (BASELINE.json configs[4] shape family) on one device.
+"""Synthetic FFN-only decode stack (the shape family of the benchmark's full-stack config) on one device.
 
     embed -> [ rmsnorm -> (dense SwiGLU | MoE layer) -> residual add ] x L -> rmsnorm -> lm_head -> argmax
 

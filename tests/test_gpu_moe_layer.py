@@ -76,13 +76,13 @@ def test_group_128_and_no_shared_expert(dev):
 
 
 def test_config0_decode_layer(dev):
-    # BASELINE configs[0]: hidden 2048, 64 experts, top-4, 1 shared, inter 1024, gs 32, batch 1, seed 0
+    # smallest benchmark config: hidden 2048, 64 experts, top-4, 1 shared, inter 1024, gs 32, batch 1, seed 0
     layer = synth_layer(0, hidden=2048, inter=1024, n_experts=64, k=4, gs=32, distinct_experts=8)
     check_layer(dev, layer, synth_tokens(0, 1, 2048), taps=True)
 
 
 def test_config1_shapes_zipf_decode_and_small_batches(dev):
-    # BASELINE configs[1]/[2] layer shapes (hidden 6144, 256 experts, top-8, inter 2048); the
+    # headline and batched-decode layer shapes (hidden 6144, 256 experts, top-8, inter 2048); the
     # experts reuse 4 weight blobs on the host, the device holds 256 separate copies
     layer = synth_layer(1, hidden=6144, inter=2048, n_experts=256, k=8, gs=32, zipf=True, distinct_experts=4)
     ml = upload_layer(dev, layer)
@@ -182,7 +182,7 @@ def test_large_batch_tile_kernel_matches_oracle_bit_for_bit(dev, monkeypatch, gs
 
 
 def test_prefill_chunk_config3_shapes_matches_oracle(dev):
-    # BASELINE configs[3] layer shapes with a 384-token chunk (the oracle needs ~10 s for it):
+    # prefill config layer shapes with a 384-token chunk (the oracle needs ~10 s for it):
     # large-batch routing (selection grid + pair layout) and the CTA-tiled kernel, compared bit
     # for bit; 4096-token chunks are covered by the size-independent property below
     layer = synth_layer(3, hidden=6144, inter=2048, n_experts=256, k=8, gs=32, zipf=True, distinct_experts=4)

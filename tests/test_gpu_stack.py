@@ -1,5 +1,5 @@
 """Greedy token ids of the synthetic FFN-only decode stack over 256 steps: the device loop must
-pick exactly the ids the CPU oracle picks (BASELINE configs[4] parity rule), on a scaled-down
+pick exactly the ids the CPU oracle picks (the full-stack parity rule), on a scaled-down
 stack (1 dense + 3 MoE layers) that the oracle finishes in seconds."""
 import numpy as np
 import pytest
