@@ -175,12 +175,13 @@ PGB_EXPORT int coli_cuda_init(const int *devices, int count) {
         if (!select_ctx(c) || !cuda_ok(cudaGetDeviceProperties(&prop, device), "device properties") ||
             !cuda_ok(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking), "stream creation") ||
             !cuda_ok(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking), "stream creation") ||
-            !cuda_ok(cudaMalloc(&c->err_dev, 256), "error word allocation") ||
-            !cuda_ok(cudaMemset(c->err_dev, 0, 256), "error word clear")) {
+            !cuda_ok(cudaHostAlloc((void **)&c->err_dev, 256, cudaHostAllocMapped | cudaHostAllocPortable),
+                     "error word allocation")) {
             g_nctx++;
             coli_cuda_shutdown();
             return 0;
         }
+        std::memset(c->err_dev, 0, 256);
         c->sms = prop.multiProcessorCount;
         c->smem_optin = prop.sharedMemPerBlockOptin;
         g_nctx++;
@@ -205,7 +206,7 @@ PGB_EXPORT void coli_cuda_shutdown(void) {
                           &c->pin_y};
         for (DevBuf *b : bufs) free_buf(*b);
         for (DevBuf &b : c->pipe) free_buf(b);
-        if (c->err_dev) cudaFree(c->err_dev);
+        if (c->err_dev) cudaFreeHost(c->err_dev);
         if (c->side) cudaStreamDestroy(c->side);
         if (c->stream) cudaStreamDestroy(c->stream);
         *c = Ctx();
@@ -257,11 +258,9 @@ PGB_EXPORT void coli_cuda_graph_cache_stats(uint64_t *captures, uint64_t *replay
 PGB_EXPORT int coli_cuda_last_device_error(int device) {
     Ctx *c = find_ctx(device);
     if (!select_ctx(c)) return -1;
-    int v = 0;
-    if (!cuda_ok(cudaStreamSynchronize(c->stream), "error word sync") ||
-        !cuda_ok(cudaMemcpy(&v, c->err_dev, sizeof(int), cudaMemcpyDeviceToHost), "error word read"))
-        return -1;
-    if (v) cudaMemset(c->err_dev, 0, sizeof(int));
+    if (!cuda_ok(cudaStreamSynchronize(c->stream), "error word sync")) return -1;
+    const int v = *static_cast<volatile int *>(c->err_dev);
+    if (v) *static_cast<volatile int *>(c->err_dev) = 0;
     return v;
 }
 PGB_EXPORT uint64_t coli_cuda_kernel_launches(void) { return g_launches.load(); }
@@ -798,10 +797,9 @@ static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const
     ok = cuda_ok(cudaStreamSynchronize(c->stream), "group synchronize") && ok;
     if (ok) std::memcpy(red ? (void *)red->out : (void *)y, c->pin_y.p, out_bytes);
     if (ok) {
-        int dev_err = 0;
-        cudaMemcpy(&dev_err, c->err_dev, sizeof(int), cudaMemcpyDeviceToHost);
+        const int dev_err = *static_cast<volatile int *>(c->err_dev);
         if (dev_err) {
-            cudaMemset(c->err_dev, 0, sizeof(int));
+            *static_cast<volatile int *>(c->err_dev) = 0;
             std::fprintf(stderr, "[CUDA] expert group: device reported error %d\n", dev_err);
             ok = 0;
         }

@@ -65,6 +65,12 @@ __device__ __forceinline__ float exp32(float v) { return __double2float_rn(exp((
 __device__ __forceinline__ float sigmoid32(float v) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, exp32(-v))); }
 __device__ __forceinline__ float silu32(float v) { return __fdiv_rn(v, __fadd_rn(1.0f, exp32(-v))); }
 
+// The per-device error word lives in page-locked host memory that the device can address, so the
+// host reads it after a synchronise without queueing a copy.  It is only written on a failure.
+__device__ __forceinline__ void report_error(int *err, int code) {
+    *reinterpret_cast<volatile int *>(err) = code;
+    __threadfence_system();
+}
 // Error codes written to the per-device error word.
 enum : int { kErrNone = 0, kErrBarrierTimeout = 1 };
 
@@ -449,7 +455,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
         {
             const bool ok = mbar_wait_bounded(bar_u32 + stage * 8, parity);
             if (__any_sync(0xffffffffu, !ok)) {
-                if (lane == 0) atomicExch(P.err, kErrBarrierTimeout);
+                if (lane == 0) report_error(P.err, kErrBarrierTimeout);
                 failed = true;
                 break;
             }
@@ -1662,7 +1668,7 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
         }
         if (chain && !failed) A.logits[(long long)(s0 + sl) * A.E + e0 + el] = acc;
     }
-    if (failed && lane == 0) atomicExch(A.err, kErrBarrierTimeout);
+    if (failed && lane == 0) report_error(A.err, kErrBarrierTimeout);
     // ---------------- the last chain CTA to finish plans the layer
     __threadfence();
     __syncthreads();

@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
         {
             const bool ok = mbar_wait_bounded(bar_u32 + stage * 8, parity);
             if (__any_sync(0xffffffffu, !ok)) {
-                if (lane == 0) atomicExch(P.err, kErrBarrierTimeout);
+                if (lane == 0) report_error(P.err, kErrBarrierTimeout);
                 failed = true;
                 break;
             }

@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) ffn_w4a8_tile_kernel(const Ge
         {
             const bool ok = mbar_wait_bounded(bar_u32 + stage * 8, (chunk / kTileStages) & 1u);
             if (__any_sync(0xffffffffu, !ok)) {
-                if (lane == 0) atomicExch(P.err, kErrBarrierTimeout);
+                if (lane == 0) report_error(P.err, kErrBarrierTimeout);
                 fail_chunk = chunk;
                 break;
             }

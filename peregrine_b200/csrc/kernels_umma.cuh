@@ -449,7 +449,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) ffn_w4a8_umma_kernel(const Gemv
         }
     }
     // ---- common tail: wait for the tensor core to go quiet, then free the tensor memory
-    if (*fail && tid == 0) atomicExch(P.err, kErrBarrierTimeout);
+    if (*fail && tid == 0) report_error(P.err, kErrBarrierTimeout);
     if (*fail && tid == 96) {
         // MMAs may still be running: a commit on a barrier of its own arrives when they are done
         const uint32_t drain_b = bar0 + 112;
