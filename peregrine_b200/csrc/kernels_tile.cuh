@@ -39,6 +39,21 @@ __device__ __forceinline__ void mma_u8s8_c(int (&d)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
 }
 
+// Two accumulators of one weight row (neighbouring activation columns) take one fold step:
+// (a0, a1) += sc * ((float)bits(c0, c1) - K).  The subtraction and the multiplication use the packed
+// fp32 pair instructions of sm_100 (each lane rounded exactly as the scalar instruction would); the
+// additions stay scalar, because the assembler contracts a packed multiply feeding a packed add
+// into a fused multiply-add even when both carry an explicit rounding mode, which would round once
+// where the reference rounds twice (crates/peregrine-kernels/src/idot.rs:98-110).
+__device__ __forceinline__ void fold_pair(float &a0, float &a1, int c0, int c1, float sc, float K) {
+    asm("{\n\t.reg .b64 cc, kk, ss, ff, pp;\n\t.reg .f32 p0, p1;\n\t"
+        "mov.b64 cc, {%2, %3};\n\tmov.b64 kk, {%5, %5};\n\tmov.b64 ss, {%4, %4};\n\t"
+        "sub.rn.f32x2 ff, cc, kk;\n\tmul.rn.f32x2 pp, ff, ss;\n\t"
+        "mov.b64 {p0, p1}, pp;\n\tadd.rn.f32 %0, %0, p0;\n\tadd.rn.f32 %1, %1, p1;\n\t}"
+        : "+f"(a0), "+f"(a1)
+        : "r"(c0), "r"(c1), "f"(sc), "f"(K));
+}
+
 // Row blocks of at most kTileTokens rows, slot by slot: an upper bound for the launch grid.
 __host__ __device__ inline int tile_row_blocks_max(int pairs_max, int slots_max) {
     return (pairs_max + kTileTokens - 1) / kTileTokens + slots_max;
@@ -111,13 +126,10 @@ __device__ __forceinline__ void tile_chunk(const uint8_t *st, int wo, int g, int
                                                                       kChunkSlabBytes);
                     const float sc_lo = sp[g * GPC + gi], sc_hi = sp[(g + 8) * GPC + gi];
 #pragma unroll
-                    for (int nt = 0; nt < NTC; ++nt)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                                const float d = __fsub_rn(__int_as_float(c[h][mt][nt][i]), kMagicF);
-                            acc[h][mt][nt][i] =
-                                __fadd_rn(acc[h][mt][nt][i], __fmul_rn(i < 2 ? sc_lo : sc_hi, d));
-                        }
+                    for (int nt = 0; nt < NTC; ++nt) {
+                        fold_pair(acc[h][mt][nt][0], acc[h][mt][nt][1], c[h][mt][nt][0], c[h][mt][nt][1], sc_lo, kMagicF);
+                        fold_pair(acc[h][mt][nt][2], acc[h][mt][nt][3], c[h][mt][nt][2], c[h][mt][nt][3], sc_hi, kMagicF);
+                    }
                 }
         } else {
 #pragma unroll
