@@ -254,6 +254,12 @@ int coli_cuda_pipe_gemm_noalloc(ColiCudaTensor *t, float *y_dev, const float *x_
 /* Device error word of a context: 0 when no kernel reported a problem since the
  * last call; otherwise the code (1 = a bounded wait on a copy barrier expired). */
 int coli_cuda_last_device_error(int device);
+/* Self-test of the failure path every kernel of this library shares: launches one CTA that waits,
+ * with a limit of `limit_cycles` clock cycles, on a copy barrier that nothing will ever complete;
+ * the wait gives up, the kernel reports code 1 through the device error word and returns, and the
+ * context stays usable.  Returns 1 when the launch and its synchronise succeeded (the caller then
+ * reads coli_cuda_last_device_error).  No counterpart in the reference. */
+int coli_cuda_selftest_bounded_wait(int device, long long limit_cycles);
 /* Number of this library's kernels launched since init (all devices). */
 uint64_t coli_cuda_kernel_launches(void);
 /* The context's stream as a cudaStream_t, for callers that order their own work. */

@@ -263,6 +263,13 @@ PGB_EXPORT int coli_cuda_last_device_error(int device) {
     if (v) *static_cast<volatile int *>(c->err_dev) = 0;
     return v;
 }
+PGB_EXPORT int coli_cuda_selftest_bounded_wait(int device, long long limit_cycles) {
+    Ctx *c = find_ctx(device);
+    if (!select_ctx(c) || limit_cycles < 1 || limit_cycles > 2000000000LL) return 0;
+    return launch(selftest_bounded_wait_kernel, dim3(1), dim3(32), 0, c->stream, "bounded-wait self-test launch",
+                  limit_cycles, c->err_dev) &&
+           cuda_ok(cudaStreamSynchronize(c->stream), "bounded-wait self-test synchronise");
+}
 PGB_EXPORT uint64_t coli_cuda_kernel_launches(void) { return g_launches.load(); }
 PGB_EXPORT void *coli_cuda_stream(int device) {
     Ctx *c = find_ctx(device);

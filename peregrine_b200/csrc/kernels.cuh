@@ -161,6 +161,23 @@ constexpr int kStageBytes = 2 * kChunkMaxBytes;  // two half-warp chunks
 constexpr int kRingBytes = kGemvWarps * kGemvStages * kStageBytes;
 constexpr int kGemvBarBytes = ((kGemvWarps * kGemvStages * 8 + 127) / 128) * 128;
 
+// The wait every kernel here uses, with the limit as a parameter, on a barrier that never
+// completes: exercises give-up, error report and a clean return.
+__global__ void selftest_bounded_wait_kernel(long long limit_cycles, int *err) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const long long t0 = clock64();
+    bool done = false;
+    while (!(done = mbar_try_wait(b, 0u)))
+        if (clock64() - t0 > limit_cycles) break;
+    if (!done && threadIdx.x == 0) report_error(err, kErrBarrierTimeout);
+}
+
 // Bounded wait on an mbarrier phase; false after ~2e9 cycles.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;

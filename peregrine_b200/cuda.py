@@ -45,7 +45,7 @@ SYMBOLS = [
     "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_set_spec", "coli_cuda_moe_layer_last_pairs",
     "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_moe_layer_ep_partial_dev",
     "coli_cuda_moe_layer_ep_combine_dev", "coli_cuda_moe_layer_set_profile", "coli_cuda_moe_layer_profile",
-    "coli_cuda_pipe_gemm_noalloc", "coli_cuda_pipe_embed", "coli_cuda_pipe_argmax", "coli_cuda_last_device_error", "coli_cuda_kernel_launches", "coli_cuda_stream",
+    "coli_cuda_pipe_gemm_noalloc", "coli_cuda_pipe_embed", "coli_cuda_pipe_argmax", "coli_cuda_last_device_error", "coli_cuda_selftest_bounded_wait", "coli_cuda_kernel_launches", "coli_cuda_stream",
 ]
 
 
@@ -131,6 +131,7 @@ def lib():
         L.coli_cuda_moe_layer_set_profile.argtypes = [vp, i]
         L.coli_cuda_moe_layer_profile.argtypes = [vp, vp, vp]
         L.coli_cuda_last_device_error.argtypes = [i]
+        L.coli_cuda_selftest_bounded_wait.argtypes = [i, C.c_longlong]
         L.coli_cuda_kernel_launches.restype = u64
         L.coli_cuda_stream.argtypes = [i]
         L.coli_cuda_stream.restype = vp
@@ -214,6 +215,11 @@ def kernel_launches() -> int:
 
 def last_device_error(device: int) -> int:
     return int(lib().coli_cuda_last_device_error(device))
+
+
+def selftest_bounded_wait(device: int, limit_cycles: int = 200_000) -> bool:
+    """Runs the bounded-wait self-test kernel; the expired wait shows up in ``last_device_error``."""
+    return lib().coli_cuda_selftest_bounded_wait(device, int(limit_cycles)) == 1
 
 
 # ------------------------------------------------------------ residency
