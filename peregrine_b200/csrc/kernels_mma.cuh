@@ -19,7 +19,10 @@
 
 namespace pgb {
 
-constexpr int kMmaWarps = 8;
+#ifndef PGB_MMA_WARPS
+#define PGB_MMA_WARPS 8
+#endif
+constexpr int kMmaWarps = PGB_MMA_WARPS;
 constexpr int kMmaThreads = kMmaWarps * 32;
 // a stage holds two 16-row weight chunks, the pass's activation rows of the same chunk
 // (chunk-major layout, 272 bytes per row) and their 8 block sums each
@@ -36,6 +39,37 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Exact int -> float without a conversion instruction: an MMA accumulator that starts from the bit
+// pattern of 1.5 * 2^23 (plus the integer -8*sum(q) correction) reads, as a float, 12582912 + d for
+// |d| < 2^22; subtracting 12582912.0f gives (float)d exactly.
+constexpr uint32_t kMagicBits = 0x4B400000u;  // 1.5 * 2^23
+constexpr float kMagicF = 12582912.0f;
+
+// d = a * b + c with c in registers of its own, so a group's first MMA can start from a constant
+// without first copying it into the destination.
+__device__ __forceinline__ void mma_u8s8_c(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1, int c0, int c1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
+}
+
+// Two accumulators of one weight row (neighbouring activation columns) take one fold step:
+// (a0, a1) += sc * ((float)bits(c0, c1) - K).  The subtraction and the multiplication use the packed
+// fp32 pair instructions of sm_100 (each lane rounded exactly as the scalar instruction would); the
+// additions stay scalar, because the assembler contracts a packed multiply feeding a packed add
+// into a fused multiply-add even when both carry an explicit rounding mode, which would round once
+// where the reference rounds twice (crates/peregrine-kernels/src/idot.rs:98-110).
+__device__ __forceinline__ void fold_pair(float &a0, float &a1, int c0, int c1, float sc, float K) {
+    asm("{\n\t.reg .b64 cc, kk, ss, ff, pp;\n\t.reg .f32 p0, p1;\n\t"
+        "mov.b64 cc, {%2, %3};\n\tmov.b64 kk, {%5, %5};\n\tmov.b64 ss, {%4, %4};\n\t"
+        "sub.rn.f32x2 ff, cc, kk;\n\tmul.rn.f32x2 pp, ff, ss;\n\t"
+        "mov.b64 {p0, p1}, pp;\n\tadd.rn.f32 %0, %0, p0;\n\tadd.rn.f32 %1, %1, p1;\n\t}"
+        : "+f"(a0), "+f"(a1)
+        : "r"(c0), "r"(c1), "f"(sc), "f"(K));
 }
 
 // NT = 8-row activation groups per pass (rows per pass = 8 * NT).  Activations come in the
@@ -98,7 +132,6 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
     // accumulators: [half][n-tile][fragment slot]; slot i: row g + 8*(i>>1), column 2t + (i&1)
     float acc[2][NT][4];
     int iacc[2][NT][4];
-    int csacc[NT][2];   // per-row format: running -8*sum over the whole K, columns 2t, 2t+1
     bool failed = false;
 
     while (cc.i < total) {
@@ -130,22 +163,27 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                         acc[h][nt][i] = 0.0f;
                         iacc[h][nt][i] = 0;
                     }
-                csacc[nt][0] = csacc[nt][1] = 0;
             }
         }
         const uint8_t *st = ring + stage * STAGE_BYTES;
 #pragma unroll
         for (int gi = 0; gi < GPC; ++gi) {
             int c[2][NT][4];
+            // -8 * sum(q) of the group's blocks per activation column of this lane; the first MMA of
+            // the group starts from bits(1.5 * 2^23) + that correction (grouped formats) or from it
+            // alone (per-row format, integer accumulation over the whole K)
+            int csg[NT][2], cinit[NT][2];
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int nt = 0; nt < NT; ++nt) {
+                csg[nt][0] = csg[nt][1] = 0;
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
+                for (int b = 0; b < BPG; ++b)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) c[h][nt][i] = 0;
-            int csg[NT][2];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) csg[nt][0] = csg[nt][1] = 0;
+                    for (int j = 0; j < 2; ++j)
+                        csg[nt][j] += *reinterpret_cast<const int *>(st + CS_OFF + ((8 * nt + 2 * t + j) * kChunkBlocks + gi * BPG + b) * 4);
+                cinit[nt][0] = (GROUPED ? (int)kMagicBits : 0) + csg[nt][0];
+                cinit[nt][1] = (GROUPED ? (int)kMagicBits : 0) + csg[nt][1];
+            }
 #pragma unroll
             for (int b = 0; b < BPG; ++b) {
                 const int blk = gi * BPG + b;
@@ -156,9 +194,6 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                     const uint8_t *xr = st + X_OFF + (8 * nt + g) * kXqChunkRowBytes + blk * 32 + 4 * t;
                     b0[nt] = *reinterpret_cast<const uint32_t *>(xr);
                     b1[nt] = *reinterpret_cast<const uint32_t *>(xr + 16);
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-                        csg[nt][j] += *reinterpret_cast<const int *>(st + CS_OFF + ((8 * nt + 2 * t + j) * kChunkBlocks + blk) * 4);
                 }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -168,7 +203,12 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                     const uint32_t a0 = w0 & 0x0F0F0F0Fu, a2 = (w0 >> 4) & 0x0F0F0F0Fu;
                     const uint32_t a1 = w1 & 0x0F0F0F0Fu, a3 = (w1 >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) mma_u8s8(c[h][nt], a0, a1, a2, a3, b0[nt], b1[nt]);
+                    for (int nt = 0; nt < NT; ++nt) {
+                        if (b == 0)
+                            mma_u8s8_c(c[h][nt], a0, a1, a2, a3, b0[nt], b1[nt], cinit[nt][0], cinit[nt][1]);
+                        else
+                            mma_u8s8(c[h][nt], a0, a1, a2, a3, b0[nt], b1[nt]);
+                    }
                 }
             }
             if (GROUPED) {
@@ -177,12 +217,13 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                     const float *sp = reinterpret_cast<const float *>(st + h * kChunkMaxBytes + kChunkSlabBytes);
                     const float sc_lo = sp[g * GPC + gi], sc_hi = sp[(g + 8) * GPC + gi];
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
+                    for (int nt = 0; nt < NT; ++nt) {
+                        fold_pair(acc[h][nt][0], acc[h][nt][1], c[h][nt][0], c[h][nt][1], sc_lo, kMagicF);
+                        fold_pair(acc[h][nt][2], acc[h][nt][3], c[h][nt][2], c[h][nt][3], sc_hi, kMagicF);
+                        if (TAP) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int d = c[h][nt][i] + csg[nt][i & 1];
-                            acc[h][nt][i] = __fadd_rn(acc[h][nt][i], __fmul_rn(i < 2 ? sc_lo : sc_hi, (float)d));
-                            if (TAP) {
+                            for (int i = 0; i < 4; ++i) {
+                                const int d = c[h][nt][i] - (int)kMagicBits;
                                 const int ridx = cc.pass * RMAX + 8 * nt + 2 * t + (i & 1);
                                 const int r = g + 8 * (i >> 1);
                                 const int o = (P.mode == 0) ? cc.tile * 16 + r : (2 * cc.tile + h) * 16 + r;
@@ -195,12 +236,12 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                                 }
                             }
                         }
+                    }
                 }
             } else {
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    csacc[nt][0] += csg[nt][0];
-                    csacc[nt][1] += csg[nt][1];
+                    // the block corrections entered through the MMA's start value
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -217,7 +258,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                 if (GROUPED) return __fmul_rn(acc[h][nt][i], sxa);
                 const float *rsp = (P.mode == 0 && h) ? cc.b_rs : cc.a_rs;
                 const float rs = (o < P.ntile * 16) ? rsp[o] : 0.0f;
-                const int d = iacc[h][nt][i] + csacc[nt][i & 1];
+                const int d = iacc[h][nt][i];  // block corrections included (they rode in the MMA start values)
                 if (TAP && P.tap != nullptr && o < P.O && (h == 0 || cc.b)) {
                     const int ridx = cc.pass * RMAX + 8 * nt + 2 * t + (i & 1);
                     if (ridx < cc.nrows) {

@@ -26,33 +26,6 @@ constexpr int kTileXOff = kTileWBytes;
 constexpr int kTileCsOff = kTileXOff + kTileTokens * kXqChunkRowBytes;
 constexpr int kTileStageBytes = kTileCsOff + kTileTokens * kChunkBlocks * 4;
 constexpr int kTileSmemBytes = kTileStages * kTileStageBytes + 128;
-constexpr uint32_t kMagicBits = 0x4B400000u;  // 1.5 * 2^23
-constexpr float kMagicF = 12582912.0f;
-
-// d = a * b + c with c in registers of its own, so a group's first MMA can start from a constant
-// without first copying it into the destination.
-__device__ __forceinline__ void mma_u8s8_c(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                           uint32_t b1, int c0, int c1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
-        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
-}
-
-// Two accumulators of one weight row (neighbouring activation columns) take one fold step:
-// (a0, a1) += sc * ((float)bits(c0, c1) - K).  The subtraction and the multiplication use the packed
-// fp32 pair instructions of sm_100 (each lane rounded exactly as the scalar instruction would); the
-// additions stay scalar, because the assembler contracts a packed multiply feeding a packed add
-// into a fused multiply-add even when both carry an explicit rounding mode, which would round once
-// where the reference rounds twice (crates/peregrine-kernels/src/idot.rs:98-110).
-__device__ __forceinline__ void fold_pair(float &a0, float &a1, int c0, int c1, float sc, float K) {
-    asm("{\n\t.reg .b64 cc, kk, ss, ff, pp;\n\t.reg .f32 p0, p1;\n\t"
-        "mov.b64 cc, {%2, %3};\n\tmov.b64 kk, {%5, %5};\n\tmov.b64 ss, {%4, %4};\n\t"
-        "sub.rn.f32x2 ff, cc, kk;\n\tmul.rn.f32x2 pp, ff, ss;\n\t"
-        "mov.b64 {p0, p1}, pp;\n\tadd.rn.f32 %0, %0, p0;\n\tadd.rn.f32 %1, %1, p1;\n\t}"
-        : "+f"(a0), "+f"(a1)
-        : "r"(c0), "r"(c1), "f"(sc), "f"(K));
-}
 
 // Row blocks of at most kTileTokens rows, slot by slot: an upper bound for the launch grid.
 __host__ __device__ inline int tile_row_blocks_max(int pairs_max, int slots_max) {
