@@ -20,7 +20,7 @@
 namespace pgb {
 
 #ifndef PGB_MMA_WARPS
-#define PGB_MMA_WARPS 8
+#define PGB_MMA_WARPS 10
 #endif
 constexpr int kMmaWarps = PGB_MMA_WARPS;
 constexpr int kMmaThreads = kMmaWarps * 32;
