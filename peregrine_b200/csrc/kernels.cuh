@@ -147,6 +147,37 @@ __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ 
     }
 }
 
+// Pair-ordered copy of already quantised token rows for the tensor-core kernels: output row p is
+// token pair_token[p], in the chunk-major layout (pcap > 0) or the core-matrix layout (pcap < 0)
+// described at qrow_i8_kernel.  Quantising once per token and copying int8 rows replaces
+// quantising every (token, expert) pair from fp32 again.  One CTA per pair row.
+__global__ void __launch_bounds__(256) gather_pair_rows_kernel(const int8_t *__restrict__ xq_tok,
+                                                               const int *__restrict__ cs_tok,
+                                                               const float *__restrict__ sx_tok, int kp, int nblk,
+                                                               const int *__restrict__ pair_token,
+                                                               const int *__restrict__ n_pairs_dev,
+                                                               int8_t *__restrict__ xqp, int *__restrict__ csp,
+                                                               float *__restrict__ sxp, long long pcap) {
+    const int p = blockIdx.x;
+    if (p >= *n_pairs_dev) return;
+    const int tok = pair_token[p];
+    const long long cap = pcap < 0 ? -pcap : pcap;
+    const uint4 *src = reinterpret_cast<const uint4 *>(xq_tok + (long long)tok * kp);
+    for (int u = threadIdx.x; u < (kp >> 4); u += blockDim.x) {
+        const int chunk = u >> 4, unit = u & 15;
+        const long long off = pcap < 0 ? ((((long long)chunk * 16 + unit) * cap + p) << 4)
+                                       : ((long long)chunk * cap + p) * kXqChunkRowBytes + unit * 16;
+        *reinterpret_cast<uint4 *>(xqp + off) = __ldg(src + u);
+    }
+    const int nchunk = nblk >> 3;
+    const int4 *csrc = reinterpret_cast<const int4 *>(cs_tok + (long long)tok * nblk);
+    for (int u = threadIdx.x; u < 2 * nchunk; u += blockDim.x) {
+        const int chunk = u >> 1;
+        *reinterpret_cast<int4 *>(csp + ((long long)chunk * cap + p) * kChunkBlocks + (u & 1) * 4) = __ldg(csrc + u);
+    }
+    if (threadIdx.x == 0) sxp[p] = sx_tok[tok];
+}
+
 // ------------------------------------------------------------ int4 x int8 GEMV
 #ifndef PGB_GEMV_WARPS
 #define PGB_GEMV_WARPS 12
