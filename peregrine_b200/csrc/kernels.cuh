@@ -1185,11 +1185,14 @@ constexpr int kRtThreads = 288;  // 9 warps
 constexpr int kRtRingBytes = 160 * 1024;   // the ring uses as many stages as fit here (at most 16)
 constexpr int kRtBarOffset = kRtRingBytes; // barriers and flags follow the ring
 // slice length along D: long slices for a single token (fewer hand-overs on the critical chain)
+// tokens per chain CTA: 32 (one chain per thread) up to 32 tokens, above that 64 (two independent
+// chains per thread fill the issue slots a single dependent chain leaves empty)
+__host__ __device__ inline int route_tokens_per_cta(int M) { return M > kRtMT ? 2 * kRtMT : kRtMT; }
 __host__ __device__ inline int route_slice(int M) { return M == 1 ? 512 : 256; }
 // floats per operand row inside a stage: 16-byte skew so the 8 router rows land on distinct banks
 __host__ __device__ inline int route_row_floats(int M) { return route_slice(M) + 4; }
 __host__ __device__ inline int route_stage_bytes(int M) {
-    return (kRtEPB + (M < kRtMT ? M : kRtMT)) * route_row_floats(M) * 4;
+    return (kRtEPB + (M < route_tokens_per_cta(M) ? M : route_tokens_per_cta(M))) * route_row_floats(M) * 4;
 }
 __host__ __device__ inline int route_stages(int M) {
     const int n = kRtRingBytes / route_stage_bytes(M);
@@ -1214,6 +1217,10 @@ struct RouteArgs {
     int *xcs;
     int kp, nblk;
     int *err;
+    // Operands re-laid for batches: rwt[e-block][slice][8][260] and xt[slice][M][260] (rows of 256
+    // floats + 4 of padding, route_tile_rows_kernel), so a slice's 8 router rows and a CTA's token
+    // rows are one bulk copy each instead of one per row; nullptr: copy row by row
+    const float *rwt, *xt;
     int small_plan;   // route_fused_kernel: at most kSpecTokens tokens on one device: route_plan_small<true>
     int no_plan;      // route_fused_kernel: logits and quantised rows only (large batches plan separately)
     float spec_sign;  // route_spec_kernel: -1 turns the speculative pick upside down (repair-path self-test)
@@ -1412,6 +1419,19 @@ __device__ __forceinline__ void route_plan_small(const float *__restrict__ logit
     }
 }
 
+// Slice-major copy of fp32 rows for the batch router: dst[((r / G) * nslice + slice) * G + r % G][260]
+// holds src[r][slice * 256 ..] (zero past D and for rows past `rows`); 4 floats of padding per
+// row keep the 8 router rows of a stage on distinct shared-memory banks.  grid = (rows_padded, nslice).
+__global__ void __launch_bounds__(64) route_tile_rows_kernel(const float *__restrict__ src, long long ld, int rows,
+                                                             int D, int G, float *__restrict__ dst) {
+    const int r = blockIdx.x, slice = blockIdx.y, nslice = gridDim.y;
+    float *out = dst + (((long long)(r / G) * nslice + slice) * G + (r % G)) * 260;
+    for (int j = threadIdx.x; j < 260; j += blockDim.x) {
+        const int d = slice * 256 + j;
+        out[j] = (j < 256 && d < D && r < rows) ? src[(long long)r * ld + d] : 0.0f;
+    }
+}
+
 // Quantiser role of the routing launches (crates/peregrine-kernels/src/quant.rs:14-33): one CTA
 // turns token `row` into int8 with its scale and the -8*sum correction of every 32-block.
 __device__ __forceinline__ void route_quantise_row(const RouteArgs &A, int row, unsigned char *rt_smem) {
@@ -1504,8 +1524,9 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
     // ---------------- chain role
     const int n_eblk = (A.E + kRtEPB - 1) / kRtEPB;
     const int eb = blockIdx.x % n_eblk, sb = blockIdx.x / n_eblk;
-    const int e0 = eb * kRtEPB, s0 = sb * kRtMT;
-    const int ne = min(kRtEPB, A.E - e0), ns = min(kRtMT, A.M - s0);
+    const int tpc = route_tokens_per_cta(A.M);
+    const int e0 = eb * kRtEPB, s0 = sb * tpc;
+    const int ne = min(kRtEPB, A.E - e0), ns = min(tpc, A.M - s0);
     const int kRtStages = route_stages(A.M), kRtStageBytes = route_stage_bytes(A.M);
     const int kRtSL = route_slice(A.M), kRtRowFloats = route_row_floats(A.M);
     const int xrow0 = kRtEPB;  // token rows follow the 8 router rows inside a stage
@@ -1538,6 +1559,21 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
             }
             const int d0 = i * kRtSL;
             const int dlen = min(kRtSL, A.D - d0);
+            if (A.xt != nullptr && A.M > 1) {
+                // two copies per slice: the e-block's 8 padded router rows, the CTA's padded token rows
+                if (lane == 0) {
+                    fence_proxy_async();
+                    mbar_expect_tx(full_u32 + st * 8, (uint32_t)((kRtEPB + ns) * kRtRowFloats * 4));
+                    bulk_g2s(smem_u32(rt_smem + st * kRtStageBytes),
+                             A.rwt + ((long long)eb * nslice + i) * kRtEPB * kRtRowFloats,
+                             (uint32_t)(kRtEPB * kRtRowFloats * 4), full_u32 + st * 8);
+                    bulk_g2s(smem_u32(rt_smem + st * kRtStageBytes + xrow0 * kRtRowFloats * 4),
+                             A.xt + ((long long)i * A.M + s0) * kRtRowFloats, (uint32_t)(ns * kRtRowFloats * 4),
+                             full_u32 + st * 8);
+                }
+                __syncwarp();
+                continue;
+            }
             if (lane == 0) {
                 fence_proxy_async();
                 mbar_expect_tx(full_u32 + st * 8, (uint32_t)(rows * dlen * 4));
@@ -1648,6 +1684,51 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
                 if (lane == 0) mbar_arrive(empty_u32 + st * 8);
             }
             if (chain && !failed) A.logits[(long long)s0 * A.E + e0 + el] = acc;
+        }
+    } else if (A.M > kRtMT) {
+        // Large batch: thread (el, sl) runs the chains of expert el for tokens sl and sl + 32.  Each
+        // chain is still one strictly ordered multiply-then-add sequence; the two are independent.
+        const int el = tid & 7, sl = tid >> 3;
+        float acc0 = 0.0f, acc1 = 0.0f;
+        for (int i = 0; i < nslice; ++i) {
+            const int st = i % kRtStages;
+            const bool ok = mbar_wait_bounded(full_u32 + st * 8, (i / kRtStages) & 1u);
+            if (__any_sync(0xffffffffu, !ok)) {
+                failed = true;
+                break;
+            }
+            const float *stage = reinterpret_cast<const float *>(rt_smem + st * kRtStageBytes);
+            const float *wr = stage + el * kRtRowFloats;
+            const float *x0 = stage + (xrow0 + sl) * kRtRowFloats;
+            const float *x1 = x0 + 32 * kRtRowFloats;  // rows past the block's last token: stale, never stored
+            const int dlen = min(kRtSL, A.D - i * kRtSL);
+            if (dlen == kRtSL) {
+#pragma unroll 4
+                for (int d = 0; d < kRtSL; d += 4) {
+                    const float4 wv = *reinterpret_cast<const float4 *>(wr + d);
+                    const float4 a = *reinterpret_cast<const float4 *>(x0 + d);
+                    const float4 b = *reinterpret_cast<const float4 *>(x1 + d);
+                    acc0 = __fadd_rn(acc0, __fmul_rn(a.x, wv.x));
+                    acc1 = __fadd_rn(acc1, __fmul_rn(b.x, wv.x));
+                    acc0 = __fadd_rn(acc0, __fmul_rn(a.y, wv.y));
+                    acc1 = __fadd_rn(acc1, __fmul_rn(b.y, wv.y));
+                    acc0 = __fadd_rn(acc0, __fmul_rn(a.z, wv.z));
+                    acc1 = __fadd_rn(acc1, __fmul_rn(b.z, wv.z));
+                    acc0 = __fadd_rn(acc0, __fmul_rn(a.w, wv.w));
+                    acc1 = __fadd_rn(acc1, __fmul_rn(b.w, wv.w));
+                }
+            } else {
+                for (int d = 0; d < dlen; ++d) {
+                    acc0 = __fadd_rn(acc0, __fmul_rn(x0[d], wr[d]));
+                    acc1 = __fadd_rn(acc1, __fmul_rn(x1[d], wr[d]));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_u32 + st * 8);
+        }
+        if (!failed && el < ne) {
+            if (sl < ns) A.logits[(long long)(s0 + sl) * A.E + e0 + el] = acc0;
+            if (sl + 32 < ns) A.logits[(long long)(s0 + sl + 32) * A.E + e0 + el] = acc1;
         }
     } else {
         const int el = tid & 7, sl = tid >> 3;
