@@ -573,6 +573,7 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
     P.xq_stride = L.kp;
     P.cs_stride = L.nblk;
     P.err = c->err_dev;
+    P.neg_zero = -0.0f;
     const bool grouped = L.grouped != 0;
     if (P.tile_rb > 0) {
         if (want_quant_stage) return fail("w4a8 tile kernel: no quantising stage");

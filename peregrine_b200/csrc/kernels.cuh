@@ -266,6 +266,7 @@ struct GemvParams {
     const int *spec_a, *spec_b, *spec_ka, *spec_kb;
     int spec_n, spec_m;
     const unsigned *amax_alt;
+    float neg_zero;  // -0.0f, as a run-time value: the fold's product is an FMA onto it (see fold_pair)
     int grid;  // host only: CTAs to launch (0 = one per SM)
     int pdl;   // host only: launch with programmatic stream serialisation (see griddep_wait)
     int tile_rb;  // host only: > 0 selects the large-batch tile kernel with this many row blocks in the grid

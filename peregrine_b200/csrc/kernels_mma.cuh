@@ -57,19 +57,22 @@ __device__ __forceinline__ void mma_u8s8_c(int (&d)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
 }
 
-// Two accumulators of one weight row (neighbouring activation columns) take one fold step:
-// (a0, a1) += sc * ((float)bits(c0, c1) - K).  The subtraction and the multiplication use the packed
-// fp32 pair instructions of sm_100 (each lane rounded exactly as the scalar instruction would); the
-// additions stay scalar, because the assembler contracts a packed multiply feeding a packed add
-// into a fused multiply-add even when both carry an explicit rounding mode, which would round once
-// where the reference rounds twice (crates/peregrine-kernels/src/idot.rs:98-110).
-__device__ __forceinline__ void fold_pair(float &a0, float &a1, int c0, int c1, float sc, float K) {
-    asm("{\n\t.reg .b64 cc, kk, ss, ff, pp;\n\t.reg .f32 p0, p1;\n\t"
+// Two accumulators of one weight row (neighbouring activation columns) take one fold step,
+// (a0, a1) += sc * ((float)bits(c0, c1) - K), on the packed fp32 pair instructions of sm_100, each
+// lane rounded exactly as the scalar subtract / multiply / add of the reference would be
+// (crates/peregrine-kernels/src/idot.rs:98-110).  The product must be rounded on its own: the
+// assembler contracts a packed multiply that feeds a packed add into one fused multiply-add even
+// when both carry an explicit rounding mode, so the multiply is written as a fused multiply-add
+// onto negative zero (x + -0 = x for every x, so this *is* the rounded product) with the zero
+// taken from a kernel argument, which nothing can fold away and nothing can fuse further.
+__device__ __forceinline__ void fold_pair(float &a0, float &a1, int c0, int c1, float sc, float K, float nz) {
+    asm("{\n\t.reg .b64 cc, kk, ss, aa, ff, pp, zz;\n\t"
         "mov.b64 cc, {%2, %3};\n\tmov.b64 kk, {%5, %5};\n\tmov.b64 ss, {%4, %4};\n\t"
-        "sub.rn.f32x2 ff, cc, kk;\n\tmul.rn.f32x2 pp, ff, ss;\n\t"
-        "mov.b64 {p0, p1}, pp;\n\tadd.rn.f32 %0, %0, p0;\n\tadd.rn.f32 %1, %1, p1;\n\t}"
+        "mov.b64 aa, {%0, %1};\n\tmov.b64 zz, {%6, %6};\n\t"
+        "sub.rn.f32x2 ff, cc, kk;\n\tfma.rn.f32x2 pp, ff, ss, zz;\n\tadd.rn.f32x2 aa, aa, pp;\n\t"
+        "mov.b64 {%0, %1}, aa;\n\t}"
         : "+f"(a0), "+f"(a1)
-        : "r"(c0), "r"(c1), "f"(sc), "f"(K));
+        : "r"(c0), "r"(c1), "f"(sc), "f"(K), "f"(nz));
 }
 
 // NT = 8-row activation groups per pass (rows per pass = 8 * NT).  Activations come in the
@@ -218,8 +221,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                     const float sc_lo = sp[g * GPC + gi], sc_hi = sp[(g + 8) * GPC + gi];
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
-                        fold_pair(acc[h][nt][0], acc[h][nt][1], c[h][nt][0], c[h][nt][1], sc_lo, kMagicF);
-                        fold_pair(acc[h][nt][2], acc[h][nt][3], c[h][nt][2], c[h][nt][3], sc_hi, kMagicF);
+                        fold_pair(acc[h][nt][0], acc[h][nt][1], c[h][nt][0], c[h][nt][1], sc_lo, kMagicF, P.neg_zero);
+                        fold_pair(acc[h][nt][2], acc[h][nt][3], c[h][nt][2], c[h][nt][3], sc_hi, kMagicF, P.neg_zero);
                         if (TAP) {
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {

@@ -35,7 +35,7 @@ __host__ __device__ inline int tile_row_blocks_max(int pairs_max, int slots_max)
 // One 256-element chunk of the K extent for one warp: NTC 8-row column tiles (compile-time, so the
 // unrolled MMA / fold sequence has no branches) against 2 x 2 sixteen-row weight tiles.
 template <bool GROUPED, int BPG, int NTC>
-__device__ __forceinline__ void tile_chunk(const uint8_t *st, int wo, int g, int t, int rowoff,
+__device__ __forceinline__ void tile_chunk(const uint8_t *st, int wo, int g, int t, int rowoff, float nz,
                                            float (&acc)[2][2][4][4], int (&iacc)[2][2][4][4], int (&csacc)[4][2]) {
     constexpr int GPC = kChunkBlocks / BPG;
     const uint8_t *xb = st + kTileXOff + (rowoff + g) * kXqChunkRowBytes + 4 * t;
@@ -100,8 +100,8 @@ __device__ __forceinline__ void tile_chunk(const uint8_t *st, int wo, int g, int
                     const float sc_lo = sp[g * GPC + gi], sc_hi = sp[(g + 8) * GPC + gi];
 #pragma unroll
                     for (int nt = 0; nt < NTC; ++nt) {
-                        fold_pair(acc[h][mt][nt][0], acc[h][mt][nt][1], c[h][mt][nt][0], c[h][mt][nt][1], sc_lo, kMagicF);
-                        fold_pair(acc[h][mt][nt][2], acc[h][mt][nt][3], c[h][mt][nt][2], c[h][mt][nt][3], sc_hi, kMagicF);
+                        fold_pair(acc[h][mt][nt][0], acc[h][mt][nt][1], c[h][mt][nt][0], c[h][mt][nt][1], sc_lo, kMagicF, nz);
+                        fold_pair(acc[h][mt][nt][2], acc[h][mt][nt][3], c[h][mt][nt][2], c[h][mt][nt][3], sc_hi, kMagicF, nz);
                     }
                 }
         } else {
@@ -240,10 +240,10 @@ __global__ void __launch_bounds__(kTileThreads, 1) ffn_w4a8_tile_kernel(const Ge
         }
         const uint8_t *st = smem + stage * kTileStageBytes;
         switch (ntc) {
-            case 4: tile_chunk<GROUPED, BPG, 4>(st, wo, g, t, rowoff, acc, iacc, csacc); break;
-            case 3: tile_chunk<GROUPED, BPG, 3>(st, wo, g, t, rowoff, acc, iacc, csacc); break;
-            case 2: tile_chunk<GROUPED, BPG, 2>(st, wo, g, t, rowoff, acc, iacc, csacc); break;
-            case 1: tile_chunk<GROUPED, BPG, 1>(st, wo, g, t, rowoff, acc, iacc, csacc); break;
+            case 4: tile_chunk<GROUPED, BPG, 4>(st, wo, g, t, rowoff, P.neg_zero, acc, iacc, csacc); break;
+            case 3: tile_chunk<GROUPED, BPG, 3>(st, wo, g, t, rowoff, P.neg_zero, acc, iacc, csacc); break;
+            case 2: tile_chunk<GROUPED, BPG, 2>(st, wo, g, t, rowoff, P.neg_zero, acc, iacc, csacc); break;
+            case 1: tile_chunk<GROUPED, BPG, 1>(st, wo, g, t, rowoff, P.neg_zero, acc, iacc, csacc); break;
             default: break;
         }
     }

@@ -103,15 +103,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait_park(uint32_t bar, uint32_t pa
     return ok;
 }
 
-// fold_pair (kernels_tile.cuh) for two neighbouring columns of one activation row: the columns are
+// fold_pair (kernels_mma.cuh) for two neighbouring columns of one activation row: the columns are
 // different weight rows, so each has its own scale; the subtrahend is the row's constant.
-__device__ __forceinline__ void fold_pair2(float &a0, float &a1, int c0, int c1, float s0, float s1, float K) {
-    asm("{\n\t.reg .b64 cc, kk, ss, ff, pp;\n\t.reg .f32 p0, p1;\n\t"
+__device__ __forceinline__ void fold_pair2(float &a0, float &a1, int c0, int c1, float s0, float s1, float K,
+                                           float nz) {
+    asm("{\n\t.reg .b64 cc, kk, ss, aa, ff, pp, zz;\n\t"
         "mov.b64 cc, {%2, %3};\n\tmov.b64 kk, {%6, %6};\n\tmov.b64 ss, {%4, %5};\n\t"
-        "sub.rn.f32x2 ff, cc, kk;\n\tmul.rn.f32x2 pp, ff, ss;\n\t"
-        "mov.b64 {p0, p1}, pp;\n\tadd.rn.f32 %0, %0, p0;\n\tadd.rn.f32 %1, %1, p1;\n\t}"
+        "mov.b64 aa, {%0, %1};\n\tmov.b64 zz, {%7, %7};\n\t"
+        "sub.rn.f32x2 ff, cc, kk;\n\tfma.rn.f32x2 pp, ff, ss, zz;\n\tadd.rn.f32x2 aa, aa, pp;\n\t"
+        "mov.b64 {%0, %1}, aa;\n\t}"
         : "+f"(a0), "+f"(a1)
-        : "r"(c0), "r"(c1), "f"(s0), "f"(s1), "f"(K));
+        : "r"(c0), "r"(c1), "f"(s0), "f"(s1), "f"(K), "f"(nz));
 }
 
 // bounded wait that also gives up when another role has already failed
@@ -386,10 +388,10 @@ __global__ void __launch_bounds__(kUmThreads, 1) ffn_w4a8_umma_kernel(const Gemv
 #pragma unroll
                     for (int v = 0; v < 8; ++v) {
                         const float4 a = s0[v], b = s1[v];
-                        fold_pair2(acc[4 * v + 0], acc[4 * v + 1], d0[4 * v + 0], d0[4 * v + 1], a.x, a.y, sub);
-                        fold_pair2(acc[4 * v + 2], acc[4 * v + 3], d0[4 * v + 2], d0[4 * v + 3], a.z, a.w, sub);
-                        fold_pair2(acc[32 + 4 * v + 0], acc[32 + 4 * v + 1], d1[4 * v + 0], d1[4 * v + 1], b.x, b.y, sub);
-                        fold_pair2(acc[32 + 4 * v + 2], acc[32 + 4 * v + 3], d1[4 * v + 2], d1[4 * v + 3], b.z, b.w, sub);
+                        fold_pair2(acc[4 * v + 0], acc[4 * v + 1], d0[4 * v + 0], d0[4 * v + 1], a.x, a.y, sub, P.neg_zero);
+                        fold_pair2(acc[4 * v + 2], acc[4 * v + 3], d0[4 * v + 2], d0[4 * v + 3], a.z, a.w, sub, P.neg_zero);
+                        fold_pair2(acc[32 + 4 * v + 0], acc[32 + 4 * v + 1], d1[4 * v + 0], d1[4 * v + 1], b.x, b.y, sub, P.neg_zero);
+                        fold_pair2(acc[32 + 4 * v + 2], acc[32 + 4 * v + 3], d1[4 * v + 2], d1[4 * v + 3], b.z, b.w, sub, P.neg_zero);
                     }
                 }
             } else {
