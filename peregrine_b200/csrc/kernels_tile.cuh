@@ -40,24 +40,27 @@ __device__ __forceinline__ void tile_chunk(const uint8_t *st, int wo, int g, int
     constexpr int GPC = kChunkBlocks / BPG;
     const uint8_t *xb = st + kTileXOff + (rowoff + g) * kXqChunkRowBytes + 4 * t;
     const int *csb = reinterpret_cast<const int *>(st + kTileCsOff) + (rowoff + 2 * t) * kChunkBlocks;
-    // not unrolled: one group's MMA + fold sequence is a few hundred instructions, and the loop
-    // body has to stay inside the instruction cache
-#pragma unroll 1
-    for (int gi = 0; gi < GPC; ++gi) {
-        int c[2][2][4][4];
+
+    // the MMAs of scale group gi into c (grouped formats) or onto iacc (per-row format)
+    auto mma_group = [&](int gi, int (&c)[2][2][4][4]) {
         // -8 * sum(q) of the group's blocks, per activation column of this lane; for grouped
         // formats it rides in the MMA's start value: bits(1.5 * 2^23) + correction
-        int csg[4][2], cinit[4][2];
+        int cinit[4][2];
 #pragma unroll
         for (int nt = 0; nt < NTC; ++nt) {
-            csg[nt][0] = csg[nt][1] = 0;
+            int c0 = 0, c1 = 0;
 #pragma unroll
             for (int b = 0; b < BPG; ++b) {
-                csg[nt][0] += csb[(8 * nt) * kChunkBlocks + gi * BPG + b];
-                csg[nt][1] += csb[(8 * nt + 1) * kChunkBlocks + gi * BPG + b];
+                c0 += csb[(8 * nt) * kChunkBlocks + gi * BPG + b];
+                c1 += csb[(8 * nt + 1) * kChunkBlocks + gi * BPG + b];
             }
-            cinit[nt][0] = (int)kMagicBits + csg[nt][0];
-            cinit[nt][1] = (int)kMagicBits + csg[nt][1];
+            if (GROUPED) {
+                cinit[nt][0] = (int)kMagicBits + c0;
+                cinit[nt][1] = (int)kMagicBits + c1;
+            } else {
+                csacc[nt][0] += c0;
+                csacc[nt][1] += c1;
+            }
         }
 #pragma unroll
         for (int b = 0; b < BPG; ++b) {
@@ -90,27 +93,52 @@ __device__ __forceinline__ void tile_chunk(const uint8_t *st, int wo, int g, int
                     }
                 }
         }
-        if (GROUPED) {
+    };
+    // the fp32 fold of group gi's dots
+    auto fold_group = [&](int gi, int (&c)[2][2][4][4]) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    const float *sp = reinterpret_cast<const float *>(st + (h * 4 + 2 * wo + mt) * kChunkMaxBytes +
-                                                                      kChunkSlabBytes);
-                    const float sc_lo = sp[g * GPC + gi], sc_hi = sp[(g + 8) * GPC + gi];
+            for (int mt = 0; mt < 2; ++mt) {
+                const float *sp =
+                    reinterpret_cast<const float *>(st + (h * 4 + 2 * wo + mt) * kChunkMaxBytes + kChunkSlabBytes);
+                const float sc_lo = sp[g * GPC + gi], sc_hi = sp[(g + 8) * GPC + gi];
 #pragma unroll
-                    for (int nt = 0; nt < NTC; ++nt) {
-                        fold_pair(acc[h][mt][nt][0], acc[h][mt][nt][1], c[h][mt][nt][0], c[h][mt][nt][1], sc_lo, kMagicF, nz);
-                        fold_pair(acc[h][mt][nt][2], acc[h][mt][nt][3], c[h][mt][nt][2], c[h][mt][nt][3], sc_hi, kMagicF, nz);
-                    }
+                for (int nt = 0; nt < NTC; ++nt) {
+                    fold_pair(acc[h][mt][nt][0], acc[h][mt][nt][1], c[h][mt][nt][0], c[h][mt][nt][1], sc_lo, kMagicF, nz);
+                    fold_pair(acc[h][mt][nt][2], acc[h][mt][nt][3], c[h][mt][nt][2], c[h][mt][nt][3], sc_hi, kMagicF, nz);
                 }
-        } else {
-#pragma unroll
-            for (int nt = 0; nt < NTC; ++nt) {
-                csacc[nt][0] += csg[nt][0];
-                csacc[nt][1] += csg[nt][1];
             }
+    };
+
+    int ca[2][2][4][4];
+    if (!GROUPED) {
+        // integer accumulation over the whole K: nothing to fold per group
+#pragma unroll 1
+        for (int gi = 0; gi < GPC; ++gi) mma_group(gi, ca);
+        return;
+    }
+    if (BPG == 1) {
+        // one block per group: the first dots of a group can be folded while its last MMAs are
+        // still running, so the plain order already overlaps the two (measured faster here)
+#pragma unroll 1
+        for (int gi = 0; gi < GPC; ++gi) {
+            mma_group(gi, ca);
+            fold_group(gi, ca);
         }
+        return;
+    }
+    // Several blocks per group: a group's fold has to wait for all of its MMAs, so the MMAs of
+    // group gi + 1 are issued before group gi is folded, on two alternating result sets.  Two groups
+    // per loop trip (not more): the body has to stay inside the instruction cache.
+    int cb[2][2][4][4];
+    mma_group(0, ca);
+#pragma unroll 1
+    for (int gi = 0; gi < GPC; gi += 2) {
+        if (gi + 1 < GPC) mma_group(gi + 1, cb);
+        fold_group(gi, ca);
+        if (gi + 2 < GPC) mma_group(gi + 2, ca);
+        if (gi + 1 < GPC) fold_group(gi + 1, cb);
     }
 }
 
