@@ -323,6 +323,47 @@ __device__ __forceinline__ void cursor_next(TileCursor &c, const GemvParams &P, 
     cursor_seek<RMAX>(c, P, total, stride);
 }
 
+// Ordered combine of one 32-column tile by the warp whose arrival completes it (down launches of
+// the device-resident layer): out starts at zero, each expert's row is added as out + (w * y) in
+// batch-union order, the shared expert last (crates/peregrine-model/src/mlp.rs:111-127,
+// concurrent.rs:1866-1929).  The lists of a token are read once by the warp (lane j holds entry j;
+// k <= 32) and the rows of a token are fetched eight at a time before the first is used, so the
+// tail of the launch is a few round trips to L2 rather than one per expert.
+__device__ __forceinline__ void ordered_combine_tile(const GemvParams &P, int tile, int lane, int n_slots) {
+    __threadfence();
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) last = (atomicAdd(P.comb.col_done + tile, 1) == n_slots - 1);
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    __threadfence();
+    const int col = tile * 32 + lane;
+    const bool in = col < P.O;
+    const int sp0 = *P.comb.shared_pair0;
+    for (int s = 0; s < P.comb.M; ++s) {
+        const int ke = P.comb.keff[s];
+        const int pj = lane < P.comb.k ? P.comb.comb_pair[s * P.comb.k + lane] : 0;
+        const float wj = lane < P.comb.k ? P.comb.comb_w[s * P.comb.k + lane] : 0.0f;
+        const float ysh = (sp0 >= 0 && in) ? __ldcg(P.out + (long long)(sp0 + s) * P.out_stride + col) : 0.0f;
+        float a = 0.0f;
+        for (int j0 = 0; j0 < ke; j0 += 8) {
+            float yv[8], wv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int j = j0 + u;
+                const int p = __shfl_sync(0xffffffffu, pj, j & 31);
+                wv[u] = __shfl_sync(0xffffffffu, wj, j & 31);
+                yv[u] = (j < ke && in) ? __ldcg(P.out + (long long)p * P.out_stride + col) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (j0 + u < ke) a = __fadd_rn(a, __fmul_rn(wv[u], yv[u]));
+        }
+        if (sp0 >= 0) a = __fadd_rn(a, ysh);
+        if (in) P.comb.out[(long long)s * P.comb.ldo + col] = a;
+    }
+}
+
 // Each warp streams two 16-row tiles (lanes 0-15 / 16-31) through a private
 // ring of kGemvStages shared-memory stages filled by bulk copies of one
 // 256-element chunk each; lane L owns one weight row for the whole K extent, so
@@ -642,34 +683,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
                     if (valid && o_half < P.O) P.out[(long long)(cc.row0 + ridx) * P.out_stride + o_half] = v;
                 }
             }
-            if (P.mode == 1 && P.comb.col_done != nullptr && cc.pass == cc.npass - 1) {
-                // Ordered combine by the warp that completes an output column tile: out starts at
-                // zero, each expert's row is added as out + (w * y) in batch-union order, the shared
-                // expert last (crates/peregrine-model/src/mlp.rs:111-127, concurrent.rs:1866-1929).
-                __threadfence();
-                __syncwarp();
-                int last = 0;
-                if (lane == 0) last = (atomicAdd(P.comb.col_done + cc.tile, 1) == n_slots - 1);
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __threadfence();
-                    const int col = cc.tile * 32 + lane;
-                    const int sp0 = *P.comb.shared_pair0;
-                    if (col < P.O) {
-                        for (int s = 0; s < P.comb.M; ++s) {
-                            const int ke = P.comb.keff[s];
-                            float a = 0.0f;
-                            for (int j = 0; j < ke; ++j) {
-                                const int p = P.comb.comb_pair[s * P.comb.k + j];
-                                const float wgt = P.comb.comb_w[s * P.comb.k + j];
-                                a = __fadd_rn(a, __fmul_rn(wgt, __ldcg(P.out + (long long)p * P.out_stride + col)));
-                            }
-                            if (sp0 >= 0) a = __fadd_rn(a, __ldcg(P.out + (long long)(sp0 + s) * P.out_stride + col));
-                            P.comb.out[(long long)s * P.comb.ldo + col] = a;
-                        }
-                    }
-                }
-            }
+            if (P.mode == 1 && P.comb.col_done != nullptr && cc.pass == cc.npass - 1)
+                ordered_combine_tile(P, cc.tile, lane, n_slots);
         }
         cursor_next<RMAX>(cc, P, total, stride);
         ++cq;

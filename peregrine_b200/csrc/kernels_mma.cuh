@@ -313,32 +313,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                     }
                 }
             }
-            if (P.mode == 1 && P.comb.col_done != nullptr && cc.pass == cc.npass - 1) {
-                // ordered combine by the warp that completes an output column tile (see gemv_w4a8_kernel)
-                __threadfence();
-                __syncwarp();
-                int last = 0;
-                if (lane == 0) last = (atomicAdd(P.comb.col_done + cc.tile, 1) == n_slots - 1);
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __threadfence();
-                    const int col = cc.tile * 32 + lane;
-                    const int sp0 = *P.comb.shared_pair0;
-                    if (col < P.O) {
-                        for (int s = 0; s < P.comb.M; ++s) {
-                            const int ke = P.comb.keff[s];
-                            float a = 0.0f;
-                            for (int j = 0; j < ke; ++j) {
-                                const int p = P.comb.comb_pair[s * P.comb.k + j];
-                                const float wgt = P.comb.comb_w[s * P.comb.k + j];
-                                a = __fadd_rn(a, __fmul_rn(wgt, __ldcg(P.out + (long long)p * P.out_stride + col)));
-                            }
-                            if (sp0 >= 0) a = __fadd_rn(a, __ldcg(P.out + (long long)(sp0 + s) * P.out_stride + col));
-                            P.comb.out[(long long)s * P.comb.ldo + col] = a;
-                        }
-                    }
-                }
-            }
+            if (P.mode == 1 && P.comb.col_done != nullptr && cc.pass == cc.npass - 1)
+                ordered_combine_tile(P, cc.tile, lane, n_slots);
         }
         cursor_next<RMAX>(cc, P, total, stride);
         ++cq;
