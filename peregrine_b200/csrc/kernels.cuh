@@ -393,6 +393,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
     // predecessor (the repair launch) for the activation rows, see below
     griddep_launch_dependents();
     if (P.mode == 0) griddep_wait();
+    // Scalars of the plan are fetched here, together with the selections compared below, so that
+    // the dependent steps further down (slot table, staging) do not each start with a round trip
+    // of their own: after a cold start every first touch costs a microsecond.
+    const int n_slots = __ldcg(P.n_slots);
+    const int n_xrows_now = (XS == 2 && P.n_xrows_dev) ? __ldcg(P.n_xrows_dev) : P.n_xrows;
     bool spec_same = true;
     if (P.spec_a) {
         int bad = 0;
@@ -416,7 +421,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
     }
     __syncwarp();
 
-    const int n_slots = *P.n_slots;
     const int total = n_slots * P.warp_tiles;
     const int stride = gridDim.x * kGemvWarps;
 
@@ -458,26 +462,19 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
         for (int i = threadIdx.x; i < P.n_xrows; i += blockDim.x) sx_s[i] = P.sx[i];
         __syncthreads();
     } else if (XS == 2) {
-        const int nrows_valid = P.n_xrows_dev ? min(*P.n_xrows_dev, P.n_xrows) : P.n_xrows;
+        const int nrows_valid = min(n_xrows_now, P.n_xrows);
         float *inv_s = sx_s + P.n_xrows;  // scratch: 1/s per row
-        for (int row = threadIdx.x; row < nrows_valid; row += blockDim.x) {
-            const unsigned *ab = (P.amax_alt && !spec_same) ? P.amax_alt : P.amax_bits;
-            float s = __fdiv_rn(__uint_as_float(ab[row]), 127.0f);
-            if (s < 1e-12f) s = 1e-12f;
-            sx_s[row] = s;
-            inv_s[row] = __fdiv_rn(1.0f, s);
-        }
-        __syncthreads();
         // four consecutive elements per thread and step; eight neighbouring lanes cover one
         // 32-element block, so the block sum is three shuffles.  Loads of a whole step batch are
-        // issued before any of them is used.
+        // issued before any of them is used, and the first batch goes out before the row scales
+        // are known (its addresses do not depend on them).
         const int q4_per_row = P.xq_stride >> 2;
         const int total4 = nrows_valid * q4_per_row;
         const bool vec_ok = ((P.x_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(P.x_f32) & 15) == 0);
         constexpr int kBatch = 12;  // a decode step's 9 rows of 2048 are one batch: a single round trip to L2
-        for (int base4 = 0; base4 < total4; base4 += kBatch * kGemvThreads) {
-            float4 v[kBatch];
-            int rowv[kBatch], c4v[kBatch];
+        float4 v[kBatch];
+        int rowv[kBatch], c4v[kBatch];
+        auto load_batch = [&](int base4) {
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
                 const int i4 = base4 + u * kGemvThreads + (int)threadIdx.x;
@@ -499,6 +496,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
                     }
                 }
             }
+        };
+        auto quant_batch = [&]() {
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
                 // all 32 lanes take part in the shuffles; lanes past the end carry zeros
@@ -518,6 +517,20 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
                     if ((c4v[u] & 7) == 0) cs_s[rowv[u] * P.cs_stride + (c4v[u] >> 3)] = -8 * sum;
                 }
             }
+        };
+        load_batch(0);
+        for (int row = threadIdx.x; row < nrows_valid; row += blockDim.x) {
+            const unsigned *ab = (P.amax_alt && !spec_same) ? P.amax_alt : P.amax_bits;
+            float s = __fdiv_rn(__uint_as_float(__ldcg(ab + row)), 127.0f);
+            if (s < 1e-12f) s = 1e-12f;
+            sx_s[row] = s;
+            inv_s[row] = __fdiv_rn(1.0f, s);
+        }
+        __syncthreads();
+        quant_batch();
+        for (int base4 = kBatch * kGemvThreads; base4 < total4; base4 += kBatch * kGemvThreads) {
+            load_batch(base4);
+            quant_batch();
         }
         __syncthreads();
     }
