@@ -36,7 +36,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 // 1-D bulk copy global -> shared (TMA engine), completion counted on an mbarrier.
-// Source, destination and size must be multiples of 16 bytes.  No multicast.
+// Source, destination and size must be multiples of 16 bytes.  One destination CTA.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
