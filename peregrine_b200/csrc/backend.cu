@@ -600,10 +600,10 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
 // names the source row of each output row.
 static int qrow_run(Ctx *c, const float *x, long long ldx, int K, const W4Layout &L, int8_t *xq, float *sx, int *cs,
                     const int *n_rows_dev, int n_rows, int grid_rows, const int *rowmap = nullptr,
-                    long long pcap = 0) {
+                    long long pcap = 0, const unsigned *amax_bits = nullptr) {
     if (grid_rows < 1) return 1;
     return launch(qrow_i8_kernel, dim3(grid_rows), dim3(256), 0, c->stream, "activation quantise launch", x, ldx, K,
-                  L.kp, L.nblk, xq, sx, cs, n_rows_dev, n_rows, rowmap, pcap);
+                  L.kp, L.nblk, xq, sx, cs, n_rows_dev, n_rows, rowmap, pcap, amax_bits);
 }
 
 // ------------------------------------------------------------- expert group

@@ -91,21 +91,26 @@ constexpr int kXqChunkRowBytes = kChunkElems + 16;
 __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ x, long long ldx, int K, int kp,
                                                       int nblk, int8_t *__restrict__ xq, float *__restrict__ sx,
                                                       int *__restrict__ csum, const int *__restrict__ n_rows_dev,
-                                                      int n_rows, const int *__restrict__ rowmap, long long pcap) {
+                                                      int n_rows, const int *__restrict__ rowmap, long long pcap,
+                                                      const unsigned *__restrict__ amax_bits) {
     const int row = blockIdx.x;
     const int limit = n_rows_dev ? *n_rows_dev : n_rows;
     if (row >= limit) return;
     const float *xr = x + (long long)(rowmap ? rowmap[row] : row) * ldx;
     __shared__ float red[8];
     __shared__ float s_inv;
-    float amax = 0.0f;
-    for (int i = threadIdx.x; i < K; i += blockDim.x) {
-        float a = fabsf(xr[i]);
-        if (a > amax) amax = a;
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-        float other = __shfl_xor_sync(0xffffffffu, amax, o);
-        if (other > amax) amax = other;
+    // amax_bits (optional, indexed by output row): the row maximum the producing launch already
+    // left (bit pattern of max|x|, NaN never recorded), which saves the first pass over the row
+    float amax = amax_bits ? __uint_as_float(amax_bits[row]) : 0.0f;
+    if (!amax_bits) {
+        for (int i = threadIdx.x; i < K; i += blockDim.x) {
+            float a = fabsf(xr[i]);
+            if (a > amax) amax = a;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            float other = __shfl_xor_sync(0xffffffffu, amax, o);
+            if (other > amax) amax = other;
+        }
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) red[warp] = amax;
