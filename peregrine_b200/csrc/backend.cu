@@ -150,6 +150,15 @@ PGB_EXPORT int coli_cuda_probe_device_count(void) {
 
 PGB_EXPORT void coli_cuda_shutdown(void);
 
+// The side stream carries the exact router chains, which the down launch waits for: highest
+// priority, so its few CTAs are placed before the expert launches that run beside them.
+static cudaError_t create_side_stream(cudaStream_t *st) {
+    int lo = 0, hi = 0;
+    cudaError_t e = cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    if (e != cudaSuccess) return e;
+    return cudaStreamCreateWithPriority(st, cudaStreamNonBlocking, hi);
+}
+
 PGB_EXPORT int coli_cuda_init(const int *devices, int count) {
     int available = 0;
     if (!devices || count < 1 || count > COLI_CUDA_MAX_DEVICES) return 0;
@@ -174,7 +183,7 @@ PGB_EXPORT int coli_cuda_init(const int *devices, int count) {
         cudaDeviceProp prop{};
         if (!select_ctx(c) || !cuda_ok(cudaGetDeviceProperties(&prop, device), "device properties") ||
             !cuda_ok(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking), "stream creation") ||
-            !cuda_ok(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking), "stream creation") ||
+            !cuda_ok(create_side_stream(&c->side), "stream creation") ||
             !cuda_ok(cudaHostAlloc((void **)&c->err_dev, 256, cudaHostAllocMapped | cudaHostAllocPortable),
                      "error word allocation")) {
             g_nctx++;
