@@ -1371,9 +1371,14 @@ __device__ __forceinline__ void route_plan_small(const float *__restrict__ logit
         const int keff0 = keff_s[0], keff1 = M > 1 ? keff_s[1] : 0;
         const int e0 = lane < keff0 ? idx_s[lane] : -1;
         const int e1 = lane < keff1 ? idx_s[32 + lane] : -2;
+        // the expert-table entries are fetched now; they are needed after the scans below
+        ExpertDev ex0 = {}, ex1 = {}, exs = {};
+        if (e0 >= 0) ex0 = experts[e0];
+        if (e1 >= 0) ex1 = experts[e1];
+        if (has_shared && lane == 0) exs = experts[E];
         int dup_of = -1;           // slot of token 0 that my token-1 pick repeats
         bool shared_by_1 = false;  // my token-0 pick is repeated by token 1
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < (M > 1 ? k : 0); ++j) {
             const int o0 = __shfl_sync(0xffffffffu, e0, j), o1 = __shfl_sync(0xffffffffu, e1, j);
             if (e1 >= 0 && o0 == e1) dup_of = j;
             if (e0 >= 0 && o1 == e0) shared_by_1 = true;
@@ -1393,8 +1398,7 @@ __device__ __forceinline__ void route_plan_small(const float *__restrict__ logit
         const int nfresh = __popc(fb);
         const int nun = keff0 + nfresh, run = total_a + nfresh;
         const int row_dup = __shfl_sync(0xffffffffu, row_a, dup_of < 0 ? 0 : dup_of);
-        auto slot_of = [&](int e_id, int r0, int n, int p) {
-            const ExpertDev ex = experts[e_id];
+        auto slot_of = [&](const ExpertDev &ex, int r0, int n, int p) {
             GemvSlot g;
             g.a = ex.gate;
             g.b = ex.up;
@@ -1413,7 +1417,7 @@ __device__ __forceinline__ void route_plan_small(const float *__restrict__ logit
         };
         if (e0 >= 0) {
             plan.pair_token[row_a] = 0;
-            slot_of(e0, row_a, c0, lane);
+            slot_of(ex0, row_a, c0, lane);
             if (EXACT) {
                 plan.union_ids[lane] = e0;
                 plan.tok_pair[lane] = row_a;
@@ -1426,12 +1430,12 @@ __device__ __forceinline__ void route_plan_small(const float *__restrict__ logit
         const int row1 = fresh ? total_a + rank_b : row_dup + 1;
         if (e1 >= 0) {
             plan.pair_token[row1] = 1;
-            if (fresh) slot_of(e1, row1, 1, keff0 + rank_b);
+            if (fresh) slot_of(ex1, row1, 1, keff0 + rank_b);
         }
         if (EXACT && M > 1) {
             // combine order of token 1: its picks by ascending union position
             int pos = 0;
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < k; ++j) {
                 const int other = __shfl_sync(0xffffffffu, slot1, j);
                 pos += (other < slot1) ? 1 : 0;
             }
@@ -1443,7 +1447,7 @@ __device__ __forceinline__ void route_plan_small(const float *__restrict__ logit
             }
         }
         if (has_shared && lane < M) plan.pair_token[run + lane] = lane;
-        if (has_shared && lane == 0) slot_of(E, run, M, nun);
+        if (has_shared && lane == 0) slot_of(exs, run, M, nun);
         if (lane == 0) {
             *plan.n_union = nun;
             *plan.n_slots = nun + (has_shared ? 1 : 0);
