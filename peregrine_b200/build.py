@@ -9,7 +9,6 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcoli_cuda_backend.so")
-HOSTCHECK = os.path.join(HERE, "libpgb_hostcheck.so")
 
 SOURCES = ["backend.cu", "w4_host.cpp"]
 DEPS = ["kernels.cuh", "kernels_mma.cuh", "kernels_tile.cuh", "kernels_umma.cuh", "w4_layout.h", "w4_host.h", "backend_layer.inc", "backend_pipe.inc", "backend_noalloc.inc",
@@ -48,16 +47,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-def build_hostcheck(force: bool = False) -> str:
-    """Host-only helper library for the CPU tests of the tile-stream layout."""
-    srcs = [os.path.join(CSRC, "w4_hostcheck.cpp"), os.path.join(CSRC, "w4_host.cpp")]
-    deps = srcs + [os.path.join(CSRC, "w4_layout.h"), os.path.join(CSRC, "w4_host.h")]
-    if force or _stale(HOSTCHECK, deps):
-        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-pthread", "-o", HOSTCHECK] + srcs
-        subprocess.check_call(cmd, cwd=CSRC)
-    return HOSTCHECK
-
-
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
-    print(build_hostcheck(force="--force" in sys.argv))

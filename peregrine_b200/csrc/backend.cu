@@ -38,9 +38,15 @@ struct Ctx {
     uint64_t scratch_gen = 0;
     // expert-group scratch (grow-only, per device; one caller thread per device)
     DevBuf x, y, h, xq, sx, xcs, hq, sh, hcs, slots_gu, slots_dn, slots_f32, nslots, csr_ptr, csr_idx, csr_rw, out;
-    DevBuf pin_x, pin_y;
+    DevBuf pin_x, pin_y, pin_slots;
     DevBuf pipe[24];
     bool capturing = false;
+    // Shape cache of the expert-group call (COLI_CUDA_GRAPH=1), bookkeeping only: which launch
+    // shapes have been seen under which scratch generation (cuda/backend_cuda.cu:678-745).
+    struct ShapeSlot {
+        uint64_t key = 0, gen = 0, used = 0;
+    } shapes[16];
+    uint64_t shape_clock = 0;
 };
 
 static Ctx g_ctx[COLI_CUDA_MAX_DEVICES];
@@ -139,6 +145,35 @@ static int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, 
     return cuda_ok(cudaGetLastError(), what);
 }
 
+// Dynamic shared-memory opt-in per kernel.  cudaFuncSetAttribute applies to the current device
+// only, so the record of what has been set is kept per context slot (cleared at shutdown): the
+// attribute is (re)set whenever a launch on that device needs more than was recorded for it.
+struct SmemOptIn {
+    const void *fn;
+    int bytes;
+};
+static std::vector<SmemOptIn> g_smem_optin[COLI_CUDA_MAX_DEVICES];
+static std::mutex g_smem_mu;
+
+template <typename K>
+static int ensure_smem(Ctx *c, K kernel, size_t bytes, const char *what) {
+    if (bytes <= 48 * 1024) return 1;
+    const void *fn = reinterpret_cast<const void *>(kernel);
+    std::lock_guard<std::mutex> lk(g_smem_mu);
+    std::vector<SmemOptIn> &tab = g_smem_optin[c - g_ctx];
+    for (SmemOptIn &e : tab)
+        if (e.fn == fn) {
+            if (e.bytes >= (int)bytes) return 1;
+            if (!cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), what))
+                return 0;
+            e.bytes = (int)bytes;
+            return 1;
+        }
+    if (!cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), what)) return 0;
+    tab.push_back({fn, (int)bytes});
+    return 1;
+}
+
 PGB_EXPORT int coli_cuda_probe_device_count(void) {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess) {
@@ -212,13 +247,15 @@ PGB_EXPORT void coli_cuda_shutdown(void) {
         DevBuf *bufs[] = {&c->x,        &c->y,        &c->h,         &c->xq,     &c->sx,      &c->xcs,
                           &c->hq,       &c->sh,       &c->hcs,       &c->slots_gu, &c->slots_dn, &c->slots_f32,
                           &c->nslots,   &c->csr_ptr,  &c->csr_idx,   &c->csr_rw, &c->out,     &c->pin_x,
-                          &c->pin_y};
+                          &c->pin_y,    &c->pin_slots};
         for (DevBuf *b : bufs) free_buf(*b);
         for (DevBuf &b : c->pipe) free_buf(b);
         if (c->err_dev) cudaFreeHost(c->err_dev);
         if (c->side) cudaStreamDestroy(c->side);
         if (c->stream) cudaStreamDestroy(c->stream);
         *c = Ctx();
+        std::lock_guard<std::mutex> lk(g_smem_mu);
+        g_smem_optin[i].clear();
     }
     g_nctx = 0;
     t_current_device = -1;
@@ -426,14 +463,7 @@ static size_t gemv_xs_bytes(int n_xrows, int kp, int nblk) {
 template <int RMAX, bool GROUPED, int BPG, int XS, bool TAP>
 static int gemv_launch_t(Ctx *c, const GemvParams &P, size_t smem) {
     auto kfn = gemv_w4a8_kernel<RMAX, GROUPED, BPG, XS, TAP>;
-    static std::atomic<uint32_t> configured{0};  // one bit per device slot
-    const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
-    if (!(configured.load() & bit)) {
-        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c->smem_optin),
-                     "gemv shared-memory opt-in"))
-            return 0;
-        configured.fetch_or(bit);
-    }
+    if (!ensure_smem(c, kfn, c->smem_optin, "gemv shared-memory opt-in")) return 0;
     if (P.pdl)
         return launch_pdl(kfn, dim3(P.grid > 0 ? P.grid : c->sms), dim3(kGemvThreads), smem, c->stream,
                           "w4a8 gemv launch", P);
@@ -470,14 +500,7 @@ template <int NT, bool GROUPED, int BPG, bool TAP>
 static int mma_launch_t(Ctx *c, const GemvParams &P) {
     auto kfn = gemv_w4a8_mma_kernel<NT, GROUPED, BPG, TAP>;
     const size_t smem = (size_t)mma_ring_bytes(NT) + kMmaBarBytes;
-    static std::atomic<uint32_t> configured{0};
-    const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
-    if (!(configured.load() & bit)) {
-        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                     "mma gemv shared-memory opt-in"))
-            return 0;
-        configured.fetch_or(bit);
-    }
+    if (!ensure_smem(c, kfn, smem, "mma gemv shared-memory opt-in")) return 0;
     return launch(kfn, dim3(c->sms), dim3(kMmaThreads), smem, c->stream, "w4a8 mma gemv launch", P);
 }
 
@@ -517,14 +540,7 @@ static bool gemv_can_quant_stage(Ctx *c, int n_xrows, const W4Layout &L, int max
 template <bool GROUPED, int BPG>
 static int tile_launch_t(Ctx *c, const GemvParams &P) {
     auto kfn = ffn_w4a8_tile_kernel<GROUPED, BPG>;
-    static std::atomic<uint32_t> configured{0};
-    const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
-    if (!(configured.load() & bit)) {
-        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemBytes),
-                     "tile kernel shared-memory opt-in"))
-            return 0;
-        configured.fetch_or(bit);
-    }
+    if (!ensure_smem(c, kfn, (size_t)kTileSmemBytes, "tile kernel shared-memory opt-in")) return 0;
     const int n_oblk = (P.mode == 0) ? (P.ntile + 3) / 4 : (P.ntile + 7) / 8;
     return launch(kfn, dim3(n_oblk, P.tile_rb), dim3(kTileThreads), (size_t)kTileSmemBytes, c->stream,
                   "w4a8 tile kernel launch", P);
@@ -532,14 +548,7 @@ static int tile_launch_t(Ctx *c, const GemvParams &P) {
 template <bool GROUPED, int BPG>
 static int umma_launch_t(Ctx *c, const GemvParams &P) {
     auto kfn = ffn_w4a8_umma_kernel<GROUPED, BPG>;
-    static std::atomic<uint32_t> configured{0};
-    const uint32_t bit = 1u << (uint32_t)(c - g_ctx);
-    if (!(configured.load() & bit)) {
-        if (!cuda_ok(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kUmSmemBytes),
-                     "tcgen05 kernel shared-memory opt-in"))
-            return 0;
-        configured.fetch_or(bit);
-    }
+    if (!ensure_smem(c, kfn, (size_t)kUmSmemBytes, "tcgen05 kernel shared-memory opt-in")) return 0;
     const int n_oblk = (P.mode == 0) ? (P.ntile + 3) / 4 : (P.ntile + 7) / 8;
     return launch(kfn, dim3(n_oblk, P.tile_rb), dim3(kUmThreads), (size_t)kUmSmemBytes, c->stream,
                   "w4a8 tcgen05 kernel launch", P);
@@ -604,6 +613,40 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
     return gemv_launch_r<2>(c, P, grouped, L.bpg, xs, smem);
 }
 
+// Loads and configures every kernel a single-matrix product (down-style launch, no taps, no
+// quantising stage) of this weight format can reach, whatever the row count: the dp4a kernel for 1
+// and 2 rows with and without staged activations, the tensor-core kernel for 8 and 16 rows per
+// pass, the quantiser and the slot writer.  After this no later call on the device meets a first-use
+// module load or a shared-memory opt-in for these kernels.
+template <bool GROUPED, int BPG>
+static int gemm_prepare_t(Ctx *c) {
+    cudaFuncAttributes fa;
+    int ok = 1;
+    auto touch = [&](auto kfn, size_t smem, const char *what) {
+        ok = ok && ensure_smem(c, kfn, smem, what) &&
+             cuda_ok(cudaFuncGetAttributes(&fa, reinterpret_cast<const void *>(kfn)), what);
+    };
+    touch(gemv_w4a8_kernel<1, GROUPED, BPG, 0, false>, c->smem_optin, "gemv preparation");
+    touch(gemv_w4a8_kernel<1, GROUPED, BPG, 1, false>, c->smem_optin, "gemv preparation");
+    touch(gemv_w4a8_kernel<2, GROUPED, BPG, 0, false>, c->smem_optin, "gemv preparation");
+    touch(gemv_w4a8_kernel<2, GROUPED, BPG, 1, false>, c->smem_optin, "gemv preparation");
+    touch(gemv_w4a8_mma_kernel<1, GROUPED, BPG, false>, (size_t)mma_ring_bytes(1) + kMmaBarBytes, "mma gemv preparation");
+    touch(gemv_w4a8_mma_kernel<2, GROUPED, BPG, false>, (size_t)mma_ring_bytes(2) + kMmaBarBytes, "mma gemv preparation");
+    touch(qrow_i8_kernel, 0, "quantiser preparation");
+    touch(write_slot_kernel, 0, "slot writer preparation");
+    return ok;
+}
+static int gemm_prepare(Ctx *c, const W4Layout &L) {
+    if (!L.grouped) return gemm_prepare_t<false, 1>(c);
+    switch (L.bpg) {
+        case 1: return gemm_prepare_t<true, 1>(c);
+        case 2: return gemm_prepare_t<true, 2>(c);
+        case 4: return gemm_prepare_t<true, 4>(c);
+        case 8: return gemm_prepare_t<true, 8>(c);
+    }
+    return fail("w4a8 gemv: unsupported group size");
+}
+
 // Quantises `grid_rows` (at most) fp32 rows.  pcap > 0 writes the chunk-major layout with that row
 // capacity (tensor-core kernel), else the row-major layout (dp4a kernel).  rowmap (device, optional)
 // names the source row of each output row.
@@ -616,6 +659,60 @@ static int qrow_run(Ctx *c, const float *x, long long ldx, int K, const W4Layout
 }
 
 // ------------------------------------------------------------- expert group
+// Shape cache counters of the reference's COLI_CUDA_GRAPH knob (cuda/backend_cuda.cu:678-745,
+// 1110-1166).  The launch sequence of this backend is a handful of kernels whose arguments all
+// come from device tables, so no graph is instantiated: a call takes the same path with the knob
+// on or off and its result is bit-identical.  What the caller can observe through
+// coli_cuda_graph_cache_stats is kept as the reference keeps it, as bookkeeping: the key is an
+// FNV-1a hash of the launch shape (arm, count, D, I, the reduce / tile word, rows[]); the first
+// call at a shape under the current scratch generation counts as a capture, a repeat as a
+// replay; an entry recorded before any scratch buffer of the device grew is dropped on its next
+// lookup and counted as an invalidation (the call then counts as a capture again); 16 entries per
+// device, least recently used evicted; a call the reference would not cache (its W4A16 arm, or
+// profiling on) counts as uncacheable.
+static uint64_t shape_key(int arm, int count, int D, int I, const int *rows, long long extra) {
+    uint64_t h = 1469598103934665603ULL;
+    auto mix = [&h](uint64_t v) {
+        for (int b = 0; b < 8; ++b) {
+            h ^= (v >> (b * 8)) & 0xFF;
+            h *= 1099511628211ULL;
+        }
+    };
+    mix((uint64_t)arm);
+    mix((uint64_t)count);
+    mix((uint64_t)D);
+    mix((uint64_t)I);
+    mix((uint64_t)extra);
+    for (int c = 0; c < count; ++c) mix((uint64_t)rows[c]);
+    return h ? h : 1;  // 0 marks an empty entry
+}
+// Books one graph-knob call; the caller holds g_stats_mu.
+static void shape_cache_note(Ctx *c, uint64_t key) {
+    for (Ctx::ShapeSlot &e : c->shapes) {
+        if (e.key != key) continue;
+        if (e.gen == c->scratch_gen) {
+            e.used = ++c->shape_clock;
+            g_replays++;
+            return;
+        }
+        e.key = 0;  // recorded against scratch that has since moved
+        g_invalidations++;
+        break;
+    }
+    Ctx::ShapeSlot *victim = &c->shapes[0];
+    for (Ctx::ShapeSlot &e : c->shapes) {
+        if (!e.key) {
+            victim = &e;
+            break;
+        }
+        if (e.used < victim->used) victim = &e;
+    }
+    victim->key = key;
+    victim->gen = c->scratch_gen;
+    victim->used = ++c->shape_clock;
+    g_captures++;
+}
+
 struct ReduceSpec {
     const int *row_ptr, *row_idx;
     const float *rw;
@@ -629,7 +726,7 @@ static bool same_class(const ColiCudaTensor *a, const ColiCudaTensor *b) {
 
 static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups, ColiCudaTensor *const *downs,
                              const int *rows, int count, float *y, const float *x, const ReduceSpec *red,
-                             int *arm_out) {
+                             int *arm_out, int tile_word = 0) {
     if (!gates || !ups || !downs || !rows || !x || count < 1 || count > 256) return 0;
     if (!red && !y) return 0;
     if (red && (!red->row_ptr || !red->row_idx || !red->rw || !red->out || red->s_n < 1)) return 0;
@@ -669,9 +766,6 @@ static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const
         !reserve(c, c->xq, (size_t)total * kpx * 17 / 16 + 512) || !reserve(c, c->sx, (size_t)total * 4) ||
         !reserve(c, c->xcs, (size_t)total * (kpx / 32) * 4) || !reserve(c, c->hq, (size_t)total * kph * 17 / 16 + 512) ||
         !reserve(c, c->sh, (size_t)total * 4) || !reserve(c, c->hcs, (size_t)total * (kph / 32) * 4) ||
-        !reserve(c, c->slots_gu, (size_t)count * sizeof(GemvSlot)) ||
-        !reserve(c, c->slots_dn, (size_t)count * sizeof(GemvSlot)) ||
-        !reserve(c, c->slots_f32, (size_t)count * sizeof(F32Slot)) || !reserve(c, c->nslots, 256) ||
         !reserve(c, c->pin_x, xb, true) || !reserve(c, c->pin_y, xb, true))
         return 0;
     const int profile = env_flag("COLI_CUDA_PROFILE", 0);
@@ -685,107 +779,89 @@ static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const
     ok = ok && cuda_ok(cudaMemcpyAsync(c->x.p, c->pin_x.p, xb, cudaMemcpyHostToDevice, c->stream), "group x upload");
     if (profile) cudaEventRecord(ev[1], c->stream);
 
-    // ---- phase 1: gate/up (+ SwiGLU) into h, one launch per format class
-    std::vector<char> done(count, 0);
-    for (int lead = 0; ok && lead < count; ++lead) {
-        if (done[lead]) continue;
-        const ColiCudaTensor *cls = gates[lead];
-        std::vector<GemvSlot> gs_host;
-        std::vector<F32Slot> fs_host;
-        int cls_max = 0;
-        for (int j = lead; j < count; ++j) {
-            if (done[j] || !same_class(gates[j], cls)) continue;
-            done[j] = 1;
-            cls_max = rows[j] > cls_max ? rows[j] : cls_max;
-            if (cls->kind == 0) {
-                fs_host.push_back({(const float *)gates[j]->data, (const float *)ups[j]->data, row0[j], rows[j]});
-            } else {
-                gs_host.push_back({(const uint8_t *)gates[j]->data, (const uint8_t *)ups[j]->data,
-                                   gates[j]->row_scales, ups[j]->row_scales, row0[j], rows[j]});
+    // ---- slot tables of every format class of both phases, built up front in one page-locked
+    // block (count at +0, table at +16 of each class's region) and uploaded with a single
+    // asynchronous copy ahead of the first launch: nothing in this call waits for the stream
+    // before the final synchronise.
+    struct ClassLaunch {
+        int phase;  // 0: gate/up, 1: down
+        const ColiCudaTensor *cls;
+        int cls_max, n;
+        size_t off;  // byte offset of the region inside the block
+    };
+    std::vector<ClassLaunch> classes;
+    std::vector<unsigned char> blob;
+    for (int phase = 0; phase < 2; ++phase) {
+        ColiCudaTensor *const *lead_of = phase == 0 ? gates : downs;
+        std::vector<char> done(count, 0);
+        for (int lead = 0; lead < count; ++lead) {
+            if (done[lead]) continue;
+            const ColiCudaTensor *cls = lead_of[lead];
+            ClassLaunch cl{phase, cls, 0, 0, (blob.size() + 255) & ~(size_t)255};
+            blob.resize(cl.off + 16);
+            for (int j = lead; j < count; ++j) {
+                if (done[j] || !same_class(lead_of[j], cls)) continue;
+                done[j] = 1;
+                cl.cls_max = rows[j] > cl.cls_max ? rows[j] : cl.cls_max;
+                cl.n++;
+                const size_t at = blob.size();
+                if (cls->kind == 0) {
+                    const F32Slot f = phase == 0 ? F32Slot{(const float *)gates[j]->data, (const float *)ups[j]->data,
+                                                           row0[j], rows[j]}
+                                                 : F32Slot{(const float *)downs[j]->data, nullptr, row0[j], rows[j]};
+                    blob.resize(at + sizeof(F32Slot));
+                    std::memcpy(blob.data() + at, &f, sizeof(F32Slot));
+                } else {
+                    const GemvSlot g = phase == 0
+                                           ? GemvSlot{(const uint8_t *)gates[j]->data, (const uint8_t *)ups[j]->data,
+                                                      gates[j]->row_scales, ups[j]->row_scales, row0[j], rows[j]}
+                                           : GemvSlot{(const uint8_t *)downs[j]->data, nullptr, downs[j]->row_scales,
+                                                      nullptr, row0[j], rows[j]};
+                    blob.resize(at + sizeof(GemvSlot));
+                    std::memcpy(blob.data() + at, &g, sizeof(GemvSlot));
+                }
             }
-        }
-        if (cls->kind == 0) {
-            const int n = (int)fs_host.size();
-            // slot tables are consumed asynchronously: stage through a synchronous copy into a
-            // region no earlier launch of this call still reads (one region per class is enough
-            // because every class launch is ordered on the same stream after the copy)
-            ok = ok && cuda_ok(cudaStreamSynchronize(c->stream), "group slot sync") &&
-                 cuda_ok(cudaMemcpy(c->slots_f32.p, fs_host.data(), n * sizeof(F32Slot), cudaMemcpyHostToDevice),
-                         "group slot upload") &&
-                 launch(gemv_f32_kernel, dim3((I + 7) / 8, cls_max, n), dim3(256), 0, c->stream,
-                        "f32 gate/up launch", (const F32Slot *)c->slots_f32.p, n, 0, I, D, (const float *)c->x.p,
-                        (long long)D, (float *)c->h.p, (long long)I, cls_max);
-        } else {
-            const int n = (int)gs_host.size();
-            const W4Layout &L = cls->L;
-            ok = ok && cuda_ok(cudaStreamSynchronize(c->stream), "group slot sync") &&
-                 cuda_ok(cudaMemcpy(c->slots_gu.p, gs_host.data(), n * sizeof(GemvSlot), cudaMemcpyHostToDevice),
-                         "group slot upload") &&
-                 cuda_ok(cudaMemcpy(c->nslots.p, &n, sizeof(int), cudaMemcpyHostToDevice), "group slot count") &&
-                 qrow_run(c, (const float *)c->x.p, D, D, L, (int8_t *)c->xq.p, (float *)c->sx.p, (int *)c->xcs.p,
-                          nullptr, total, total, nullptr, gemv_uses_mma(cls_max) ? total : 0);
-            GemvParams P{};
-            P.slots = (const GemvSlot *)c->slots_gu.p;
-            P.n_slots = (const int *)c->nslots.p;
-            P.xq = (const int8_t *)c->xq.p;
-            P.csum = (const int *)c->xcs.p;
-            P.sx = (const float *)c->sx.p;
-            P.rowmap = nullptr;
-            P.n_xrows = total;
-            P.pcap = total;
-            P.out = (float *)c->h.p;
-            P.out_stride = I;
-            ok = ok && gemv_run(c, P, L, 0, cls_max);
+            std::memcpy(blob.data() + cl.off, &cl.n, sizeof(int));
+            classes.push_back(cl);
         }
     }
-    // ---- phase 2: down into y, one launch per format class of the down matrices
-    std::fill(done.begin(), done.end(), 0);
-    for (int lead = 0; ok && lead < count; ++lead) {
-        if (done[lead]) continue;
-        const ColiCudaTensor *cls = downs[lead];
-        std::vector<GemvSlot> gs_host;
-        std::vector<F32Slot> fs_host;
-        int cls_max = 0;
-        for (int j = lead; j < count; ++j) {
-            if (done[j] || !same_class(downs[j], cls)) continue;
-            done[j] = 1;
-            cls_max = rows[j] > cls_max ? rows[j] : cls_max;
-            if (cls->kind == 0)
-                fs_host.push_back({(const float *)downs[j]->data, nullptr, row0[j], rows[j]});
-            else
-                gs_host.push_back(
-                    {(const uint8_t *)downs[j]->data, nullptr, downs[j]->row_scales, nullptr, row0[j], rows[j]});
+    ok = ok && reserve(c, c->slots_gu, blob.size()) && reserve(c, c->pin_slots, blob.size(), true);
+    if (ok) {
+        std::memcpy(c->pin_slots.p, blob.data(), blob.size());
+        ok = cuda_ok(cudaMemcpyAsync(c->slots_gu.p, c->pin_slots.p, blob.size(), cudaMemcpyHostToDevice, c->stream),
+                     "group slot upload");
+    }
+    // ---- phase 1: gate/up (+ SwiGLU) into h; phase 2: down into y; one launch per format class
+    for (size_t ci = 0; ok && ci < classes.size(); ++ci) {
+        const ClassLaunch &cl = classes[ci];
+        const unsigned char *region = (const unsigned char *)c->slots_gu.p + cl.off;
+        const bool up = cl.phase == 0;
+        if (cl.cls->kind == 0) {
+            ok = up ? launch(gemv_f32_kernel, dim3((I + 7) / 8, cl.cls_max, cl.n), dim3(256), 0, c->stream,
+                             "f32 gate/up launch", (const F32Slot *)(region + 16), cl.n, 0, I, D,
+                             (const float *)c->x.p, (long long)D, (float *)c->h.p, (long long)I, cl.cls_max)
+                    : launch(gemv_f32_kernel, dim3((D + 7) / 8, cl.cls_max, cl.n), dim3(256), 0, c->stream,
+                             "f32 down launch", (const F32Slot *)(region + 16), cl.n, 1, D, I, (const float *)c->h.p,
+                             (long long)I, (float *)c->y.p, (long long)D, cl.cls_max);
+            continue;
         }
-        if (cls->kind == 0) {
-            const int n = (int)fs_host.size();
-            ok = ok && cuda_ok(cudaStreamSynchronize(c->stream), "group slot sync") &&
-                 cuda_ok(cudaMemcpy(c->slots_f32.p, fs_host.data(), n * sizeof(F32Slot), cudaMemcpyHostToDevice),
-                         "group slot upload") &&
-                 launch(gemv_f32_kernel, dim3((D + 7) / 8, cls_max, n), dim3(256), 0, c->stream, "f32 down launch",
-                        (const F32Slot *)c->slots_f32.p, n, 1, D, I, (const float *)c->h.p, (long long)I,
-                        (float *)c->y.p, (long long)D, cls_max);
-        } else {
-            const int n = (int)gs_host.size();
-            const W4Layout &L = cls->L;
-            ok = ok && cuda_ok(cudaStreamSynchronize(c->stream), "group slot sync") &&
-                 cuda_ok(cudaMemcpy(c->slots_dn.p, gs_host.data(), n * sizeof(GemvSlot), cudaMemcpyHostToDevice),
-                         "group slot upload") &&
-                 cuda_ok(cudaMemcpy(c->nslots.p, &n, sizeof(int), cudaMemcpyHostToDevice), "group slot count") &&
-                 qrow_run(c, (const float *)c->h.p, I, I, L, (int8_t *)c->hq.p, (float *)c->sh.p, (int *)c->hcs.p,
-                          nullptr, total, total, nullptr, gemv_uses_mma(cls_max) ? total : 0);
-            GemvParams P{};
-            P.slots = (const GemvSlot *)c->slots_dn.p;
-            P.n_slots = (const int *)c->nslots.p;
-            P.xq = (const int8_t *)c->hq.p;
-            P.csum = (const int *)c->hcs.p;
-            P.sx = (const float *)c->sh.p;
-            P.rowmap = nullptr;
-            P.n_xrows = total;
-            P.pcap = total;
-            P.out = (float *)c->y.p;
-            P.out_stride = D;
-            ok = ok && gemv_run(c, P, L, 1, cls_max);
-        }
+        const W4Layout &L = cl.cls->L;
+        ok = up ? qrow_run(c, (const float *)c->x.p, D, D, L, (int8_t *)c->xq.p, (float *)c->sx.p, (int *)c->xcs.p,
+                           nullptr, total, total, nullptr, gemv_uses_mma(cl.cls_max) ? total : 0)
+                : qrow_run(c, (const float *)c->h.p, I, I, L, (int8_t *)c->hq.p, (float *)c->sh.p, (int *)c->hcs.p,
+                           nullptr, total, total, nullptr, gemv_uses_mma(cl.cls_max) ? total : 0);
+        GemvParams P{};
+        P.slots = (const GemvSlot *)(region + 16);
+        P.n_slots = (const int *)region;
+        P.xq = (const int8_t *)(up ? c->xq.p : c->hq.p);
+        P.csum = (const int *)(up ? c->xcs.p : c->hcs.p);
+        P.sx = (const float *)(up ? c->sx.p : c->sh.p);
+        P.rowmap = nullptr;
+        P.n_xrows = total;
+        P.pcap = total;
+        P.out = (float *)(up ? c->h.p : c->y.p);
+        P.out_stride = up ? I : D;
+        ok = ok && gemv_run(c, P, L, up ? 0 : 1, cl.cls_max);
     }
     // ---- optional CSR combine, then the result back to the host
     size_t out_bytes = xb;
@@ -835,10 +911,13 @@ static int expert_group_impl(ColiCudaTensor *const *gates, ColiCudaTensor *const
             g_kernel_ms += b;
             g_d2h_ms += d;
         }
-        // The launch sequence here is short and shape-independent, so no graph is
-        // instantiated; the cache counters are kept as bookkeeping only: with the knob
-        // on every call is counted as uncacheable.
-        if (graph_knob) g_uncacheable++;
+        if (graph_knob) {
+            if (arm != 1 && !profile && ok)
+                shape_cache_note(c, shape_key(arm, count, D, I, rows,
+                                              (long long)(red ? red->s_n : -1) * 1000003 + tile_word));
+            else
+                g_uncacheable++;
+        }
     }
     if (profile)
         for (auto &e : ev) cudaEventDestroy(e);
@@ -853,10 +932,9 @@ PGB_EXPORT int coli_cuda_expert_group(ColiCudaTensor *const *gates, ColiCudaTens
 PGB_EXPORT int coli_cuda_expert_group_tiled(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
                                             ColiCudaTensor *const *downs, const int *rows, int count, float *y,
                                             const float *x, int tile_m, int tile_n, int tile_k, int *arm_out) {
-    (void)tile_m;
-    (void)tile_n;
-    (void)tile_k;
-    return expert_group_impl(gates, ups, downs, rows, count, y, x, nullptr, arm_out);
+    // the tile only separates shape-cache entries here (one kernel family serves every tile)
+    return expert_group_impl(gates, ups, downs, rows, count, y, x, nullptr, arm_out,
+                             tile_m * 10007 + tile_n * 101 + tile_k);
 }
 PGB_EXPORT int coli_cuda_expert_group_reduce(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
                                              ColiCudaTensor *const *downs, const int *rows, int count,
@@ -874,6 +952,10 @@ PGB_EXPORT int coli_cuda_expert_mlp(ColiCudaTensor *gate, ColiCudaTensor *up, Co
 PGB_EXPORT int coli_cuda_shared_mlp_w4a16(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
                                           const float *x, int S) {
     return coli_cuda_expert_mlp(gate, up, down, y, x, S);
+}
+
+namespace pgb {
+__global__ void pipe_add_kernel(float *x, const float *t, size_t n);  // defined with the other pipe kernels
 }
 
 #include "backend_layer.inc"

@@ -754,6 +754,19 @@ __global__ void __launch_bounds__(256) gemv_f32_kernel(const F32Slot *__restrict
     (void)max_rows;
 }
 
+// One-entry slot tables written from kernel arguments: the single-matrix entry points describe
+// their launch without any host-to-device copy (a copy from a stack variable is pageable memory,
+// which a stream capture cannot record).
+__global__ void write_slot_kernel(GemvSlot *slot, int *count, const GemvSlot v) {
+    if (threadIdx.x == 0) {
+        *slot = v;
+        *count = 1;
+    }
+}
+__global__ void write_f32_slot_kernel(F32Slot *slot, const F32Slot v) {
+    if (threadIdx.x == 0) *slot = v;
+}
+
 // ------------------------------------------------------------------- router
 // Router logits, crates/peregrine-kernels/src/matmul.rs:18-30: one strictly
 // sequential, unfused fp32 chain acc = acc + x[d]*w[e,d] per (token, expert).

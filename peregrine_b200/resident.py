@@ -19,5 +19,6 @@ def upload_layer(device: int, layer: SynthLayer) -> cuda.MoeLayer:
     for e, ex in enumerate(layer.experts):
         ml.set_expert(e, upload_expert(device, ex, layer.hidden, layer.inter))
     if layer.shared is not None:
-        ml.set_shared(upload_expert(device, layer.shared, layer.hidden, layer.inter))
+        # width moe_inter * n_shared (crates/peregrine-model/src/model.rs:1838): read from the matrices
+        ml.set_shared(upload_expert(device, layer.shared, layer.hidden, layer.shared.gate.o_n))
     return ml

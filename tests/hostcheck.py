@@ -3,7 +3,25 @@ import ctypes as C
 
 import numpy as np
 
-from peregrine_b200.build import build_hostcheck
+import os
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(os.path.dirname(HERE), "peregrine_b200", "csrc")
+HOSTCHECK = os.path.join(HERE, "libpgb_hostcheck.so")
+
+
+def build_hostcheck(force: bool = False) -> str:
+    """Host-only helper library of the CPU tests: the tile-stream walk compiled from the same
+    layout header and repacker the CUDA backend uses."""
+    srcs = [os.path.join(HERE, "w4_hostcheck.cpp"), os.path.join(CSRC, "w4_host.cpp")]
+    deps = srcs + [os.path.join(CSRC, "w4_layout.h"), os.path.join(CSRC, "w4_host.h")]
+    stale = force or not os.path.exists(HOSTCHECK) or any(
+        os.path.getmtime(p) > os.path.getmtime(HOSTCHECK) for p in deps)
+    if stale:
+        subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-pthread",
+                               "-I", CSRC, "-o", HOSTCHECK] + srcs)
+    return HOSTCHECK
 
 _lib = None
 

@@ -16,6 +16,33 @@ pytestmark = pytest.mark.gpu
 REL_TOL = 1e-5  # post-scale fp32 outputs, relative
 
 
+def assert_taps(ml, layer, x, m, only_pairs=None):
+    """Per-block int32 accumulators of gate, up and down of the last forward, bit for bit against the
+    oracle's integer dots (all pairs, or the listed pair rows)."""
+    tok, exp = ml.last_pairs(m)
+    gs = layer.gs
+    ng_gu = -(-layer.hidden // gs) if gs else 1
+    ng_dn = -(-layer.inter // gs) if gs else 1
+    gu, dn = ml.read_taps(tok.size, ng_gu, ng_dn)
+    for p in (range(tok.size) if only_pairs is None else only_pairs):
+        ex = layer.shared if exp[p] == layer.n_experts else layer.experts[exp[p]]
+        g, u, d = o_expert(ex)
+        xq, sx = po.qrow_i8(x[tok[p]])
+        _, h = po.swiglu(g, u, d, x[tok[p]:tok[p] + 1], 1, want_h=True)
+        hq, sh = po.qrow_i8(h[0])
+        if gs:
+            _, bg = po.matmul_i4g_idot(xq, [sx], ex.gate.q, ex.gate.scale, 1, layer.hidden, layer.inter, gs, True)
+            _, bu = po.matmul_i4g_idot(xq, [sx], ex.up.q, ex.up.scale, 1, layer.hidden, layer.inter, gs, True)
+            _, bd = po.matmul_i4g_idot(hq, [sh], ex.down.q, ex.down.scale, 1, layer.inter, layer.hidden, gs, True)
+            assert np.array_equal(gu[p, 0], bg[0]) and np.array_equal(gu[p, 1], bu[0])
+            assert np.array_equal(dn[p], bd[0])
+        else:
+            _, ag = po.matmul_i4_idot(xq, [sx], ex.gate.q, ex.gate.scale, 1, layer.hidden, layer.inter, True)
+            _, ad = po.matmul_i4_idot(hq, [sh], ex.down.q, ex.down.scale, 1, layer.inter, layer.hidden, True)
+            assert np.array_equal(gu[p, 0, :, 0], ag[0]) and np.array_equal(dn[p, :, 0], ad[0])
+    return tok, exp
+
+
 def check_layer(dev, layer, x, taps=False):
     m = x.shape[0]
     ml = upload_layer(dev, layer)
@@ -33,27 +60,7 @@ def check_layer(dev, layer, x, taps=False):
     assert np.array_equal(bits(ml.forward(x)), bits(got))  # repeat-stable
     assert cuda.last_device_error(dev) == 0
     if taps:
-        tok, exp = ml.last_pairs(m)
-        gs = layer.gs
-        ng_gu = -(-layer.hidden // gs) if gs else 1
-        ng_dn = -(-layer.inter // gs) if gs else 1
-        gu, dn = ml.read_taps(tok.size, ng_gu, ng_dn)
-        for p in range(tok.size):
-            ex = layer.shared if exp[p] == layer.n_experts else layer.experts[exp[p]]
-            g, u, d = o_expert(ex)
-            xq, sx = po.qrow_i8(x[tok[p]])
-            _, h = po.swiglu(g, u, d, x[tok[p]:tok[p] + 1], 1, want_h=True)
-            hq, sh = po.qrow_i8(h[0])
-            if gs:
-                _, bg = po.matmul_i4g_idot(xq, [sx], ex.gate.q, ex.gate.scale, 1, layer.hidden, layer.inter, gs, True)
-                _, bu = po.matmul_i4g_idot(xq, [sx], ex.up.q, ex.up.scale, 1, layer.hidden, layer.inter, gs, True)
-                _, bd = po.matmul_i4g_idot(hq, [sh], ex.down.q, ex.down.scale, 1, layer.inter, layer.hidden, gs, True)
-                assert np.array_equal(gu[p, 0], bg[0]) and np.array_equal(gu[p, 1], bu[0])
-                assert np.array_equal(dn[p], bd[0])
-            else:
-                _, ag = po.matmul_i4_idot(xq, [sx], ex.gate.q, ex.gate.scale, 1, layer.hidden, layer.inter, True)
-                _, ad = po.matmul_i4_idot(hq, [sh], ex.down.q, ex.down.scale, 1, layer.inter, layer.hidden, True)
-                assert np.array_equal(gu[p, 0, :, 0], ag[0]) and np.array_equal(dn[p, :, 0], ad[0])
+        assert_taps(ml, layer, x, m)
     ml.free()
     return got
 
@@ -75,6 +82,16 @@ def test_group_128_and_no_shared_expert(dev):
     check_layer(dev, layer, synth_tokens(2, 6, 384), taps=True)
 
 
+@pytest.mark.parametrize("m,gs", [(1, 32), (2, 32), (5, 32), (3, 0)])
+def test_shared_expert_of_twice_the_routed_width(dev, m, gs):
+    # n_shared = 2: one shared SwiGLU of width 2 * moe_inter (crates/peregrine-model/src/model.rs:1838)
+    from peregrine_b200.synth import synth_expert
+
+    layer = synth_layer(40 + m, hidden=256, inter=96, n_experts=10, k=3, gs=gs)
+    layer.shared = synth_expert(np.random.default_rng(400 + m), 256, 192, gs)
+    check_layer(dev, layer, synth_tokens(40 + m, m, 256))
+
+
 def test_config0_decode_layer(dev):
     # smallest benchmark config: hidden 2048, 64 experts, top-4, 1 shared, inter 1024, gs 32, batch 1, seed 0
     layer = synth_layer(0, hidden=2048, inter=1024, n_experts=64, k=4, gs=32, distinct_experts=8)
@@ -89,7 +106,13 @@ def test_config1_shapes_zipf_decode_and_small_batches(dev):
     for m in (1, 4, 8, 16):
         x = synth_tokens(50 + m, m, 6144)
         want, idx, w, keff, uni = oracle_layer_forward(layer, x, threads=8, want_routing=True)
+        ml.enable_taps(m == 1)
         got = ml.forward(x)
+        if m == 1:
+            # int32 block accumulators at this shape: gate, up and down of the first and the last
+            # routed pair and of the shared expert (pair rows 0, 7 and 8 of a single token)
+            tok, exp = assert_taps(ml, layer, x, 1, only_pairs=(0, 7, 8))
+            assert exp[8] == layer.n_experts and tok.size == 9
         gidx, gw, gkeff, guni = ml.last_routing(m)
         assert np.array_equal(gidx, idx) and np.array_equal(bits(gw), bits(w)) and list(guni) == list(uni)
         assert rel_err(got, want) <= REL_TOL

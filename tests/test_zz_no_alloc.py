@@ -49,7 +49,9 @@ def test_noalloc_gemm_matches_allocating_gemm_twice(dev, gs):
     m = synth_matrix(rng, o_n, i_n, gs)
     t = (cuda.Tensor.upload_grouped(dev, m.q, m.scale, i_n, o_n, gs) if gs
          else cuda.Tensor.upload(dev, m.q, m.scale, 2, i_n, o_n))
-    for rows in (7, 3):  # two calls in a row; the second is smaller and uses other data
+    # calls in a row on the one shared array, each with other data and another row count: 7 and 3
+    # rows (tensor-core kernel, one pass), 1 and 2 (dp4a kernel, row-major scratch), 17 (two passes)
+    for rows in (7, 3, 1, 17, 2):
         x = rng.standard_normal((rows, i_n)).astype(np.float32)
         xd = DevArray(dev, x)
         y_ref = DevArray(dev, nbytes=rows * o_n * 4)
@@ -66,18 +68,28 @@ def test_noalloc_gemm_matches_allocating_gemm_twice(dev, gs):
     t.free()
 
 
-def test_noalloc_gemm_rejects_oversize_and_f32(dev):
+def test_noalloc_gemm_limit_is_143_rows_at_width_6144(dev):
+    """The largest request the 1 MiB array holds at I = 6144 is 143 rows: it is accepted and matches
+    the allocating entry point bit for bit; 144 rows are refused (0, nothing launched)."""
     lib = cuda.lib()
     rng = np.random.default_rng(5)
-    m = synth_matrix(rng, 32, 6144, 32)
-    t = cuda.Tensor.upload_grouped(dev, m.q, m.scale, 6144, 32, 32)
-    rows = 152  # one more row than the 1 MiB array can hold at this width
-    xd = DevArray(dev, nbytes=rows * 6144 * 4)
-    yd = DevArray(dev, nbytes=rows * 32 * 4)
-    assert lib.coli_cuda_pipe_gemm_noalloc(t.handle, C.c_void_p(yd.ptr), C.c_void_p(xd.ptr), rows) == 0
+    i_n, o_n = 6144, 48
+    m = synth_matrix(rng, o_n, i_n, 32)
+    t = cuda.Tensor.upload_grouped(dev, m.q, m.scale, i_n, o_n, 32)
+    rows = 143
+    x = rng.standard_normal((rows + 1, i_n)).astype(np.float32)
+    xd = DevArray(dev, x)
+    y_ref = DevArray(dev, nbytes=(rows + 1) * o_n * 4)
+    y_new = DevArray(dev, nbytes=(rows + 1) * o_n * 4)
+    assert lib.coli_cuda_pipe_gemm(t.handle, C.c_void_p(y_ref.ptr), C.c_void_p(xd.ptr), rows) == 1
+    assert lib.coli_cuda_pipe_gemm_noalloc(t.handle, C.c_void_p(y_new.ptr), C.c_void_p(xd.ptr), rows) == 1
+    want, got = y_ref.read((rows, o_n)), y_new.read((rows, o_n))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)) and np.abs(want).max() > 0
+    assert lib.coli_cuda_pipe_gemm_noalloc(t.handle, C.c_void_p(y_new.ptr), C.c_void_p(xd.ptr), rows + 1) == 0
+    assert cuda.last_device_error(dev) == 0
     f = cuda.Tensor.upload(dev, rng.standard_normal((8, 16)).astype(np.float32), None, 0, 16, 8)
-    assert lib.coli_cuda_pipe_gemm_noalloc(f.handle, C.c_void_p(yd.ptr), C.c_void_p(xd.ptr), 1) == 0
-    for b in (xd, yd):
+    assert lib.coli_cuda_pipe_gemm_noalloc(f.handle, C.c_void_p(y_new.ptr), C.c_void_p(xd.ptr), 1) == 0  # not int4
+    for b in (xd, y_ref, y_new):
         b.free()
     t.free()
     f.free()
