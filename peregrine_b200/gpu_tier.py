@@ -58,7 +58,7 @@ class GpuTier:
     def upload_expert(self, st: SafeTensors, layer: int, e: int, int4: bool | None = None) -> bool:
         """Loads one expert from the checkpoint and makes it resident; returns whether it stayed int4.
         Per-row int4 uploads raw (as the reference, gpu.rs:1359-1383); grouped int4 with a group size
-        the tile stream holds uploads raw too; anything else is dequantised to fp32."""
+        the tile stream holds (32, 64, 128, 256) uploads raw too; anything else is dequantised to fp32."""
         want_int4 = self.int4 if int4 is None else int4
         h, it = self.hidden, self.inter
         gn, un, dn = expert_names(layer, e)
@@ -66,14 +66,20 @@ class GpuTier:
         up = QtWeight.load(st, un, it, h)
         down = QtWeight.load(st, dn, h, it)
         ws = (gate, up, down)
-        per_row = all(w.fmt == QtFmt.Int4 for w in ws)
-        grouped = all(w.fmt == QtFmt.Int4Grouped for w in ws) and len({w.gs for w in ws}) == 1 and \
-            gate.gs in (32, 64, 128, 256)
-        if want_int4 and per_row:
-            ex = cuda.GpuExpert.upload_int4(self.device, gate.raw(), up.raw(), down.raw(), h, it)
-            kept = True
-        elif want_int4 and grouped:
-            ex = cuda.GpuExpert.upload_int4_grouped(self.device, gate.raw(), up.raw(), down.raw(), h, it, gate.gs)
+
+        def packable(w):
+            return w.fmt == QtFmt.Int4 or (w.fmt == QtFmt.Int4Grouped and w.gs in (32, 64, 128, 256))
+
+        # gate and up share one launch, so they must share a format; down may differ (a grouped
+        # checkpoint whose down matrix is no wider than one group is detected as per-row: one scale
+        # per row either way, and the two forms multiply the same numbers)
+        if want_int4 and all(packable(w) for w in ws) and (gate.fmt, gate.gs) == (up.fmt, up.gs):
+            def put(w):
+                if w.fmt == QtFmt.Int4:
+                    return cuda.Tensor.upload(self.device, w.q, w.scale, 2, w.i, w.o)
+                return cuda.Tensor.upload_grouped(self.device, w.q, w.scale, w.i, w.o, w.gs)
+
+            ex = cuda.GpuExpert(put(gate), put(up), put(down))
             kept = True
         else:
             ex = cuda.GpuExpert.upload(self.device, gate.dequant(), up.dequant(), down.dequant(), h, it)
