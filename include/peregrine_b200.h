@@ -203,6 +203,17 @@ int coli_cuda_moe_layer_enable_taps(ColiCudaMoeLayer *layer, int enable);
  * depend on the mode.  mode: -1 process default (on unless PEREGRINE_B200_SPEC_ROUTE=0), 0 off,
  * 1 on, 2 on with the speculative pick deliberately wrong (exercises the recompute path). */
 int coli_cuda_moe_layer_set_spec(ColiCudaMoeLayer *layer, int mode);
+/* A single token on one device with speculative routing on takes the whole step — routing, gate/up,
+ * down, ordered combine — in ONE launch of one CTA per SM (no counterpart in the reference, whose
+ * step is a host loop over kernels, cuda/backend_cuda.cu:1035-1211).  mode: -1 process default (on
+ * unless PEREGRINE_B200_FUSED_DECODE=0), 0 separate launches, 1 one launch.  Results are identical
+ * either way; taps and per-launch profiling always use the separate launches. */
+int coli_cuda_moe_layer_set_fused(ColiCudaMoeLayer *layer, int mode);
+/* Inspection of the single-launch step: with `enable` set, the next such step records 16 device
+ * timer stamps (ns) per CTA; a later call with `stamps` (capacity_ctas * 16 values) reads them back.
+ * n_ctas / n_chain report the launch's CTA count and how many of them run the exact router. */
+int coli_cuda_moe_layer_decode_timeline(ColiCudaMoeLayer *layer, int enable, unsigned long long *stamps,
+                                        int capacity_ctas, int *n_ctas, int *n_chain);
 /* pair_token[p] = token of pair row p, pair_expert[p] = expert id (E = shared). */
 int coli_cuda_moe_layer_last_pairs(ColiCudaMoeLayer *layer, int *n_pairs, int *pair_token, int *pair_expert,
                                    int capacity);

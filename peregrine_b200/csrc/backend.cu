@@ -14,6 +14,7 @@
 #include "kernels_mma.cuh"
 #include "kernels_tile.cuh"
 #include "kernels_umma.cuh"
+#include "kernels_decode.cuh"
 #include "w4_host.h"
 
 using namespace pgb;
@@ -578,7 +579,7 @@ static int tile_launch(Ctx *c, const GemvParams &P, bool grouped, int bpg) {
 // up to 2 rows run the dp4a kernel, more run the tensor-core kernel.
 // `want_quant_stage`: the caller filled x_f32 / amax_bits and wants the kernel to quantise the
 // rows itself; only valid when gemv_can_quant_stage() said so.
-static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_rows, bool want_quant_stage = false) {
+static void gemv_fill_layout(Ctx *c, GemvParams &P, const W4Layout &L, int mode) {
     P.mode = mode;
     P.nchunk = L.nchunk;
     P.chunk_bytes = L.chunk_bytes;
@@ -592,6 +593,10 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
     P.cs_stride = L.nblk;
     P.err = c->err_dev;
     P.neg_zero = -0.0f;
+}
+
+static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_rows, bool want_quant_stage = false) {
+    gemv_fill_layout(c, P, L, mode);
     const bool grouped = L.grouped != 0;
     if (P.tile_rb > 0) {
         if (want_quant_stage) return fail("w4a8 tile kernel: no quantising stage");
@@ -645,6 +650,24 @@ static int gemm_prepare(Ctx *c, const W4Layout &L) {
         case 8: return gemm_prepare_t<true, 8>(c);
     }
     return fail("w4a8 gemv: unsupported group size");
+}
+
+// The fused single-token decode step (kernels_decode.cuh): one CTA per SM.
+template <bool GROUPED, int BPG>
+static int decode_launch_t(Ctx *c, const DecodeArgs &A, size_t smem) {
+    auto kfn = decode_step_kernel<GROUPED, BPG>;
+    if (!ensure_smem(c, kfn, smem, "decode step shared-memory opt-in")) return 0;
+    return launch(kfn, dim3(c->sms), dim3(kGemvThreads), smem, c->stream, "decode step launch", A);
+}
+static int decode_launch(Ctx *c, const DecodeArgs &A, const W4Layout &L, size_t smem) {
+    if (!L.grouped) return decode_launch_t<false, 1>(c, A, smem);
+    switch (L.bpg) {
+        case 1: return decode_launch_t<true, 1>(c, A, smem);
+        case 2: return decode_launch_t<true, 2>(c, A, smem);
+        case 4: return decode_launch_t<true, 4>(c, A, smem);
+        case 8: return decode_launch_t<true, 8>(c, A, smem);
+    }
+    return fail("decode step: unsupported group size");
 }
 
 // Quantises `grid_rows` (at most) fp32 rows.  pcap > 0 writes the chunk-major layout with that row

@@ -47,6 +47,10 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
 // predecessor writes before griddep_wait().  Both are no-ops in an ordinary launch.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Bulk prefetch of a global range into L2 (source 16-byte aligned, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -291,13 +295,15 @@ struct TileCursor {
     const float *a_rs, *b_rs;
 };
 
+// `slots` is the launch's slot table: P.slots, or a table a kernel keeps in shared memory.
 template <int RMAX>
-__device__ __forceinline__ void cursor_seek(TileCursor &c, const GemvParams &P, int total, int stride) {
+__device__ __forceinline__ void cursor_seek(TileCursor &c, const GemvParams &P, const GemvSlot *slots, int total,
+                                            int stride) {
     // position on the first tile at or after c.i that has rows to compute
     while (c.i < total) {
         const int slot = c.i / P.warp_tiles;
         const int t = c.i - slot * P.warp_tiles;
-        const GemvSlot *s = P.slots + slot;
+        const GemvSlot *s = slots + slot;
         c.nrows = s->nrows;
         c.npass = (c.nrows + RMAX - 1) / RMAX;
         if (c.npass > 0) {
@@ -319,13 +325,14 @@ __device__ __forceinline__ void cursor_seek(TileCursor &c, const GemvParams &P, 
 }
 
 template <int RMAX>
-__device__ __forceinline__ void cursor_next(TileCursor &c, const GemvParams &P, int total, int stride) {
+__device__ __forceinline__ void cursor_next(TileCursor &c, const GemvParams &P, const GemvSlot *slots, int total,
+                                            int stride) {
     if (++c.chunk < P.nchunk) return;
     c.chunk = 0;
     if (++c.pass < c.npass) return;
     c.pass = 0;
     c.i += stride;
-    cursor_seek<RMAX>(c, P, total, stride);
+    cursor_seek<RMAX>(c, P, slots, total, stride);
 }
 
 // Ordered combine of one 32-column tile by the warp whose arrival completes it (down launches of
@@ -387,184 +394,189 @@ __device__ __forceinline__ void ordered_combine_tile(const GemvParams &P, int ti
 //   XS = 2: the launch's fp32 rows are quantised into shared memory by the CTA
 //           itself (crates/peregrine-kernels/src/quant.rs:14-33) from a row
 //           maximum the producing launch left in amax_bits
-template <int RMAX, bool GROUPED, int BPG, int XS, bool TAP>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvParams P) {
-    constexpr int GPC = kChunkBlocks / BPG;
-    constexpr int CHUNK_BYTES = kChunkSlabBytes + (GROUPED ? GPC * 64 : 0);
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int half = lane >> 4, r16 = lane & 15;
-    // gate/up reads its slot table from the launch before it; a down launch only depends on its
-    // predecessor (the repair launch) for the activation rows, see below
-    griddep_launch_dependents();
-    if (P.mode == 0) griddep_wait();
-    // Scalars of the plan are fetched here, together with the selections compared below, so that
-    // the dependent steps further down (slot table, staging) do not each start with a round trip
-    // of their own: after a cold start every first touch costs a microsecond.
-    const int n_slots = __ldcg(P.n_slots);
-    const int n_xrows_now = (XS == 2 && P.n_xrows_dev) ? __ldcg(P.n_xrows_dev) : P.n_xrows;
-    bool spec_same = true;
-    if (P.spec_a) {
-        int bad = 0;
-        for (int i = threadIdx.x; i < P.spec_n; i += blockDim.x) bad |= (__ldcg(P.spec_a + i) != __ldcg(P.spec_b + i));
-        for (int i = threadIdx.x; i < P.spec_m; i += blockDim.x) bad |= (__ldcg(P.spec_ka + i) != __ldcg(P.spec_kb + i));
-        spec_same = __syncthreads_or(bad) == 0;
-        if (P.mode == 0 && spec_same) return;  // the speculative launch already produced these rows
-    }
-    uint8_t *ring = smem + warp * (kGemvStages * kStageBytes);
-    const uint32_t ring_u32 = smem_u32(ring);
-    const uint32_t bar_u32 = smem_u32(smem + kRingBytes) + warp * (kGemvStages * 8);
-    int8_t *xs = reinterpret_cast<int8_t *>(smem + kRingBytes + kGemvBarBytes);
-    const int xs_bytes = (P.n_xrows * P.xq_stride + 15) & ~15;
-    int *cs_s = reinterpret_cast<int *>(xs + xs_bytes);
-    float *sx_s = reinterpret_cast<float *>(cs_s + P.n_xrows * P.cs_stride);
+//
+// The pieces below are shared by the plain GEMV launch and by the fused decode step, which runs
+// several phases (gate/up, down) over one ring without leaving the kernel.
 
+// A warp's ring and its position in the stream of work items; lives across the phases of a kernel.
+struct WarpStream {
+    uint8_t *ring;
+    uint32_t ring_u32, bar_u32;
+    uint32_t fq, cq;  // chunks fetched / consumed so far (stage = q % kGemvStages)
+    TileCursor fc, cc;
+    bool failed;
+};
+
+__device__ __forceinline__ void stream_init(WarpStream &S, uint8_t *smem, int warp, int lane) {
+    S.ring = smem + warp * (kGemvStages * kStageBytes);
+    S.ring_u32 = smem_u32(S.ring);
+    S.bar_u32 = smem_u32(smem + kRingBytes) + warp * (kGemvStages * 8);
+    S.fq = S.cq = 0;
+    S.failed = false;
     if (lane == 0) {
-        for (int s = 0; s < kGemvStages; ++s) mbar_init(bar_u32 + s * 8, 1);
+        for (int s = 0; s < kGemvStages; ++s) mbar_init(S.bar_u32 + s * 8, 1);
         fence_mbar_init();
         fence_proxy_async();
     }
     __syncwarp();
+}
 
-    const int total = n_slots * P.warp_tiles;
-    const int stride = gridDim.x * kGemvWarps;
+template <bool GROUPED, int BPG>
+__device__ __forceinline__ void stream_issue(const WarpStream &S, const TileCursor &c, uint32_t q) {
+    constexpr int CHUNK_BYTES = kChunkSlabBytes + (GROUPED ? (kChunkBlocks / BPG) * 64 : 0);
+    const uint32_t stage = q % kGemvStages;
+    const uint32_t bar = S.bar_u32 + stage * 8;
+    const uint32_t dst = S.ring_u32 + stage * kStageBytes;
+    const size_t off = (size_t)c.chunk * CHUNK_BYTES;
+    mbar_expect_tx(bar, c.b ? 2 * CHUNK_BYTES : CHUNK_BYTES);
+    bulk_g2s(dst, c.a + off, CHUNK_BYTES, bar);
+    if (c.b) bulk_g2s(dst + kChunkMaxBytes, c.b + off, CHUNK_BYTES, bar);
+}
 
-    TileCursor fc, cc;
-    fc.i = blockIdx.x + gridDim.x * warp;
-    fc.pass = 0;
-    fc.chunk = 0;
-    cursor_seek<RMAX>(fc, P, total, stride);
-    cc = fc;
-    uint32_t fq = 0, cq = 0;
+// Positions the warp on its first work item in [first, total) (items `stride` apart) and fills the
+// ring.  Everything fetched by an earlier phase must have been consumed (fq == cq).
+template <int RMAX, bool GROUPED, int BPG>
+__device__ __forceinline__ void stream_begin(WarpStream &S, const GemvParams &P, const GemvSlot *slots, int first,
+                                             int total, int stride, int lane) {
+    S.fc.i = first;
+    S.fc.pass = 0;
+    S.fc.chunk = 0;
+    cursor_seek<RMAX>(S.fc, P, slots, total, stride);
+    S.cc = S.fc;
+    if (lane == 0 && S.fc.i < total) fence_proxy_async();
+    while (S.fc.i < total && S.fq < S.cq + kGemvStages) {
+        if (lane == 0) stream_issue<GROUPED, BPG>(S, S.fc, S.fq);
+        cursor_next<RMAX>(S.fc, P, slots, total, stride);
+        ++S.fq;
+    }
+}
 
-    auto issue = [&](const TileCursor &c, uint32_t q) {
-        const uint32_t stage = q % kGemvStages;
-        const uint32_t bar = bar_u32 + stage * 8;
-        const uint32_t dst = ring_u32 + stage * kStageBytes;
-        const size_t off = (size_t)c.chunk * CHUNK_BYTES;
-        mbar_expect_tx(bar, c.b ? 2 * CHUNK_BYTES : CHUNK_BYTES);
-        bulk_g2s(dst, c.a + off, CHUNK_BYTES, bar);
-        if (c.b) bulk_g2s(dst + kChunkMaxBytes, c.b + off, CHUNK_BYTES, bar);
+// After a failed wait: give copies already in flight a bounded chance to land before the CTA retires.
+__device__ __forceinline__ void stream_drain(WarpStream &S) {
+    for (uint32_t q = S.cq; q < S.fq; ++q) {
+        const uint32_t stage = q % kGemvStages, parity = (q / kGemvStages) & 1u;
+        const long long t0 = clock64();
+        while (!mbar_try_wait(S.bar_u32 + stage * 8, parity))
+            if (clock64() - t0 > 200000000LL) break;
+    }
+    S.cq = S.fq;
+}
+
+// The XS = 2 staging: the CTA quantises `nrows_valid` fp32 rows (row stride x_ld, logical length K)
+// into shared memory as int8 rows of stride P.xq_stride with their -8*sum block corrections and
+// scales, from row maxima already known (amax_src, bit patterns, global memory).  crates/peregrine-kernels/src/quant.rs:14-33.  All threads of the CTA call it; it ends
+// with a CTA barrier.
+struct NoStamp {
+    __device__ __forceinline__ void operator()(int) const {}
+};
+template <typename Stamp = NoStamp>
+__device__ __forceinline__ void stage_quantise_rows(const GemvParams &P, const float *x_f32, long long x_ld, int K,
+                                                    int nrows_valid, const unsigned *amax_src, int8_t *xs, int *cs_s,
+                                                    float *sx_s, float *inv_s, Stamp stamp = Stamp()) {
+    // four consecutive elements per thread and step; eight neighbouring lanes cover one
+    // 32-element block, so the block sum is three shuffles.  Loads of a whole step batch are
+    // issued before any of them is used, and the first batch goes out before the row scales
+    // are known (its addresses do not depend on them).
+    const int q4_per_row = P.xq_stride >> 2;
+    const int total4 = nrows_valid * q4_per_row;
+    const bool vec_ok = ((x_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(x_f32) & 15) == 0);
+    constexpr int kBatch = 12;  // a decode step's 9 rows of 2048 are one batch: a single round trip to L2
+    float4 v[kBatch];
+    int rowv[kBatch], c4v[kBatch];
+    auto load_batch = [&](int base4) {
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int i4 = base4 + u * (int)blockDim.x + (int)threadIdx.x;
+            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            rowv[u] = -1;
+            c4v[u] = 0;
+            if (i4 < total4) {
+                const int row = i4 / q4_per_row, c4 = i4 - row * q4_per_row;
+                rowv[u] = row;
+                c4v[u] = c4;
+                const float *src = x_f32 + (long long)row * x_ld + 4 * c4;
+                if (vec_ok && 4 * c4 + 3 < K) {
+                    v[u] = __ldcg(reinterpret_cast<const float4 *>(src));
+                } else {
+                    if (4 * c4 + 0 < K) v[u].x = __ldcg(src + 0);
+                    if (4 * c4 + 1 < K) v[u].y = __ldcg(src + 1);
+                    if (4 * c4 + 2 < K) v[u].z = __ldcg(src + 2);
+                    if (4 * c4 + 3 < K) v[u].w = __ldcg(src + 3);
+                }
+            }
+        }
     };
-
-    // first fill of the ring overlaps the activation staging below
-    while (fc.i < total && fq < cq + kGemvStages) {
-        if (lane == 0) issue(fc, fq);
-        cursor_next<RMAX>(fc, P, total, stride);
-        ++fq;
-    }
-
-    // everything above (plan, weight prefetch) is independent of the preceding launch; the
-    // activation rows and their row maxima are not
-    if (P.mode != 0) griddep_wait();
-    if (XS == 1) {
-        const int n16 = xs_bytes >> 4;
-        const uint4 *src = reinterpret_cast<const uint4 *>(P.xq);
-        uint4 *dst = reinterpret_cast<uint4 *>(xs);
-        for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
-        const int ncs = P.n_xrows * P.cs_stride;
-        for (int i = threadIdx.x; i < ncs; i += blockDim.x) cs_s[i] = P.csum[i];
-        for (int i = threadIdx.x; i < P.n_xrows; i += blockDim.x) sx_s[i] = P.sx[i];
-        __syncthreads();
-    } else if (XS == 2) {
-        const int nrows_valid = min(n_xrows_now, P.n_xrows);
-        float *inv_s = sx_s + P.n_xrows;  // scratch: 1/s per row
-        // four consecutive elements per thread and step; eight neighbouring lanes cover one
-        // 32-element block, so the block sum is three shuffles.  Loads of a whole step batch are
-        // issued before any of them is used, and the first batch goes out before the row scales
-        // are known (its addresses do not depend on them).
-        const int q4_per_row = P.xq_stride >> 2;
-        const int total4 = nrows_valid * q4_per_row;
-        const bool vec_ok = ((P.x_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(P.x_f32) & 15) == 0);
-        constexpr int kBatch = 12;  // a decode step's 9 rows of 2048 are one batch: a single round trip to L2
-        float4 v[kBatch];
-        int rowv[kBatch], c4v[kBatch];
-        auto load_batch = [&](int base4) {
+    auto quant_batch = [&]() {
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int i4 = base4 + u * kGemvThreads + (int)threadIdx.x;
-                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                rowv[u] = -1;
-                c4v[u] = 0;
-                if (i4 < total4) {
-                    const int row = i4 / q4_per_row, c4 = i4 - row * q4_per_row;
-                    rowv[u] = row;
-                    c4v[u] = c4;
-                    const float *src = P.x_f32 + (long long)row * P.x_ld + 4 * c4;
-                    if (vec_ok && 4 * c4 + 3 < P.K) {
-                        v[u] = __ldcg(reinterpret_cast<const float4 *>(src));
-                    } else {
-                        if (4 * c4 + 0 < P.K) v[u].x = __ldcg(src + 0);
-                        if (4 * c4 + 1 < P.K) v[u].y = __ldcg(src + 1);
-                        if (4 * c4 + 2 < P.K) v[u].z = __ldcg(src + 2);
-                        if (4 * c4 + 3 < P.K) v[u].w = __ldcg(src + 3);
-                    }
-                }
+        for (int u = 0; u < kBatch; ++u) {
+            // all 32 lanes take part in the shuffles; lanes past the end carry zeros
+            const float inv = rowv[u] >= 0 ? inv_s[rowv[u]] : 0.0f;
+            const int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].x, inv))));
+            const int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].y, inv))));
+            const int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].z, inv))));
+            const int q3 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].w, inv))));
+            int sum = q0 + q1 + q2 + q3;
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            if (rowv[u] >= 0) {
+                const uint32_t packed = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) |
+                                        ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+                *reinterpret_cast<uint32_t *>(xs + (size_t)rowv[u] * P.xq_stride + 4 * c4v[u]) = packed;
+                if ((c4v[u] & 7) == 0) cs_s[rowv[u] * P.cs_stride + (c4v[u] >> 3)] = -8 * sum;
             }
-        };
-        auto quant_batch = [&]() {
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                // all 32 lanes take part in the shuffles; lanes past the end carry zeros
-                const float inv = rowv[u] >= 0 ? inv_s[rowv[u]] : 0.0f;
-                const int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].x, inv))));
-                const int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].y, inv))));
-                const int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].z, inv))));
-                const int q3 = max(-128, min(127, __float2int_rn(__fmul_rn(v[u].w, inv))));
-                int sum = q0 + q1 + q2 + q3;
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-                if (rowv[u] >= 0) {
-                    const uint32_t packed = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) |
-                                            ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
-                    *reinterpret_cast<uint32_t *>(xs + (size_t)rowv[u] * P.xq_stride + 4 * c4v[u]) = packed;
-                    if ((c4v[u] & 7) == 0) cs_s[rowv[u] * P.cs_stride + (c4v[u] >> 3)] = -8 * sum;
-                }
-            }
-        };
-        load_batch(0);
-        for (int row = threadIdx.x; row < nrows_valid; row += blockDim.x) {
-            const unsigned *ab = (P.amax_alt && !spec_same) ? P.amax_alt : P.amax_bits;
-            float s = __fdiv_rn(__uint_as_float(__ldcg(ab + row)), 127.0f);
-            if (s < 1e-12f) s = 1e-12f;
-            sx_s[row] = s;
-            inv_s[row] = __fdiv_rn(1.0f, s);
         }
-        __syncthreads();
+    };
+    load_batch(0);
+    for (int row = threadIdx.x; row < nrows_valid; row += blockDim.x) {
+        float s = __fdiv_rn(__uint_as_float(__ldcg(amax_src + row)), 127.0f);
+        if (s < 1e-12f) s = 1e-12f;
+        sx_s[row] = s;
+        inv_s[row] = __fdiv_rn(1.0f, s);
+    }
+    stamp(11);
+    __syncthreads();
+    stamp(12);
+    quant_batch();
+    stamp(13);
+    for (int base4 = kBatch * (int)blockDim.x; base4 < total4; base4 += kBatch * (int)blockDim.x) {
+        load_batch(base4);
         quant_batch();
-        for (int base4 = kBatch * kGemvThreads; base4 < total4; base4 += kBatch * kGemvThreads) {
-            load_batch(base4);
-            quant_batch();
-        }
-        __syncthreads();
     }
-    const int8_t *xbase = XS ? xs : P.xq;
-    const int *csbase = XS ? cs_s : P.csum;
-    const float *sxbase = XS ? sx_s : P.sx;
+    __syncthreads();
+}
 
+// Consumes the warp's items of [.., total): integer dots, fold, epilogue.  `out` / `amax_out` are
+// the phase's output rows and (mode 0, optional) row-maximum words; `on_tile_done(tile)` runs when
+// the last pass of a mode-1 item has been stored (all lanes call it).
+template <int RMAX, bool GROUPED, int BPG, int XS, bool TAP, typename OnTileDone>
+__device__ __forceinline__ void stream_run(WarpStream &S, const GemvParams &P, const GemvSlot *slots, int total,
+                                           int stride, const int8_t *xbase, const int *csbase, const float *sxbase,
+                                           float *out, unsigned *amax_out, int lane, OnTileDone on_tile_done) {
+    constexpr int GPC = kChunkBlocks / BPG;
+    const int half = lane >> 4, r16 = lane & 15;
+    TileCursor &fc = S.fc, &cc = S.cc;
     float acc[RMAX];
     int iacc[RMAX];
     int arow[RMAX];
-    bool failed = false;
 
     while (cc.i < total) {
         // keep the ring full: the stage being refilled was consumed one iteration ago
-        if (fc.i < total && fq < cq + kGemvStages) {
+        if (fc.i < total && S.fq < S.cq + kGemvStages) {
             if (lane == 0) {
                 fence_proxy_async();
-                issue(fc, fq);
+                stream_issue<GROUPED, BPG>(S, fc, S.fq);
             }
-            cursor_next<RMAX>(fc, P, total, stride);
-            ++fq;
+            cursor_next<RMAX>(fc, P, slots, total, stride);
+            ++S.fq;
         }
-        const uint32_t stage = cq % kGemvStages;
-        const uint32_t parity = (cq / kGemvStages) & 1u;
+        const uint32_t stage = S.cq % kGemvStages;
+        const uint32_t parity = (S.cq / kGemvStages) & 1u;
         {
-            const bool ok = mbar_wait_bounded(bar_u32 + stage * 8, parity);
+            const bool ok = mbar_wait_bounded(S.bar_u32 + stage * 8, parity);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) report_error(P.err, kErrBarrierTimeout);
-                failed = true;
+                S.failed = true;
                 break;
             }
         }
@@ -578,13 +590,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
                 arow[r] = P.rowmap ? P.rowmap[p] : p;
             }
         }
-        const uint8_t *wp = ring + stage * kStageBytes + half * kChunkMaxBytes + r16 * 16;
+        const uint8_t *wp = S.ring + stage * kStageBytes + half * kChunkMaxBytes + r16 * 16;
         const int o_half = (P.mode == 0) ? (cc.tile * 16 + r16) : (cc.tile * 32 + lane);
 
         float sc[GPC];
         if (GROUPED) {
             const float *sp =
-                reinterpret_cast<const float *>(ring + stage * kStageBytes + half * kChunkMaxBytes + kChunkSlabBytes) +
+                reinterpret_cast<const float *>(S.ring + stage * kStageBytes + half * kChunkMaxBytes + kChunkSlabBytes) +
                 r16 * GPC;
             if constexpr (GPC >= 4) {
 #pragma unroll
@@ -687,35 +699,86 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvPa
                     const bool store = valid && half == 0 && o_half < P.O;
                     if (store) {
                         hval = __fmul_rn(silu32(v), u);
-                        P.out[(long long)(cc.row0 + ridx) * P.out_stride + o_half] = hval;
+                        out[(long long)(cc.row0 + ridx) * P.out_stride + o_half] = hval;
                     }
-                    if (P.amax_out != nullptr) {
+                    if (amax_out != nullptr) {
                         // row maximum of |h| for the quantiser of the next launch: max is order-free,
                         // NaN never becomes the maximum (crates/peregrine-kernels/src/quant.rs:17-22)
                         float a = fabsf(hval);
                         if (!(a == a)) a = 0.0f;
                         for (int o = 8; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-                        if (valid && lane == 0 && a > 0.0f) atomicMax(P.amax_out + cc.row0 + ridx, __float_as_uint(a));
+                        if (valid && lane == 0 && a > 0.0f) atomicMax(amax_out + cc.row0 + ridx, __float_as_uint(a));
                     }
                 } else {
-                    if (valid && o_half < P.O) P.out[(long long)(cc.row0 + ridx) * P.out_stride + o_half] = v;
+                    if (valid && o_half < P.O) out[(long long)(cc.row0 + ridx) * P.out_stride + o_half] = v;
                 }
             }
-            if (P.mode == 1 && P.comb.col_done != nullptr && cc.pass == cc.npass - 1)
-                ordered_combine_tile(P, cc.tile, lane, n_slots);
+            if (P.mode == 1 && cc.pass == cc.npass - 1) on_tile_done(cc.tile);
         }
-        cursor_next<RMAX>(cc, P, total, stride);
-        ++cq;
+        cursor_next<RMAX>(cc, P, slots, total, stride);
+        ++S.cq;
     }
-    if (failed) {
-        // give copies already in flight a bounded chance to land before the CTA retires
-        for (uint32_t q = cq; q < fq; ++q) {
-            const uint32_t stage = q % kGemvStages, parity = (q / kGemvStages) & 1u;
-            const long long t0 = clock64();
-            while (!mbar_try_wait(bar_u32 + stage * 8, parity))
-                if (clock64() - t0 > 200000000LL) break;
-        }
+}
+
+template <int RMAX, bool GROUPED, int BPG, int XS, bool TAP>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_w4a8_kernel(const GemvParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // gate/up reads its slot table from the launch before it; a down launch only depends on its
+    // predecessor (the repair launch) for the activation rows, see below
+    griddep_launch_dependents();
+    if (P.mode == 0) griddep_wait();
+    // Scalars of the plan are fetched here, together with the selections compared below, so that
+    // the dependent steps further down (slot table, staging) do not each start with a round trip
+    // of their own: after a cold start every first touch costs a microsecond.
+    const int n_slots = __ldcg(P.n_slots);
+    const int n_xrows_now = (XS == 2 && P.n_xrows_dev) ? __ldcg(P.n_xrows_dev) : P.n_xrows;
+    bool spec_same = true;
+    if (P.spec_a) {
+        int bad = 0;
+        for (int i = threadIdx.x; i < P.spec_n; i += blockDim.x) bad |= (__ldcg(P.spec_a + i) != __ldcg(P.spec_b + i));
+        for (int i = threadIdx.x; i < P.spec_m; i += blockDim.x) bad |= (__ldcg(P.spec_ka + i) != __ldcg(P.spec_kb + i));
+        spec_same = __syncthreads_or(bad) == 0;
+        if (P.mode == 0 && spec_same) return;  // the speculative launch already produced these rows
     }
+    int8_t *xs = reinterpret_cast<int8_t *>(smem + kRingBytes + kGemvBarBytes);
+    const int xs_bytes = (P.n_xrows * P.xq_stride + 15) & ~15;
+    int *cs_s = reinterpret_cast<int *>(xs + xs_bytes);
+    float *sx_s = reinterpret_cast<float *>(cs_s + P.n_xrows * P.cs_stride);
+
+    WarpStream S;
+    stream_init(S, smem, warp, lane);
+    const int total = n_slots * P.warp_tiles;
+    const int stride = gridDim.x * kGemvWarps;
+    // first fill of the ring overlaps the activation staging below
+    stream_begin<RMAX, GROUPED, BPG>(S, P, P.slots, blockIdx.x + gridDim.x * warp, total, stride, lane);
+
+    // everything above (plan, weight prefetch) is independent of the preceding launch; the
+    // activation rows and their row maxima are not
+    if (P.mode != 0) griddep_wait();
+    if (XS == 1) {
+        const int n16 = xs_bytes >> 4;
+        const uint4 *src = reinterpret_cast<const uint4 *>(P.xq);
+        uint4 *dst = reinterpret_cast<uint4 *>(xs);
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+        const int ncs = P.n_xrows * P.cs_stride;
+        for (int i = threadIdx.x; i < ncs; i += blockDim.x) cs_s[i] = P.csum[i];
+        for (int i = threadIdx.x; i < P.n_xrows; i += blockDim.x) sx_s[i] = P.sx[i];
+        __syncthreads();
+    } else if (XS == 2) {
+        const unsigned *ab = (P.amax_alt && !spec_same) ? P.amax_alt : P.amax_bits;
+        stage_quantise_rows(P, P.x_f32, P.x_ld, P.K, min(n_xrows_now, P.n_xrows), ab, xs, cs_s, sx_s,
+                            sx_s + P.n_xrows);
+    }
+    const int8_t *xbase = XS ? xs : P.xq;
+    const int *csbase = XS ? cs_s : P.csum;
+    const float *sxbase = XS ? sx_s : P.sx;
+    stream_run<RMAX, GROUPED, BPG, XS, TAP>(S, P, P.slots, total, stride, xbase, csbase, sxbase, P.out, P.amax_out,
+                                            lane, [&](int tile) {
+                                                if (P.comb.col_done != nullptr)
+                                                    ordered_combine_tile(P, tile, lane, n_slots);
+                                            });
+    if (S.failed) stream_drain(S);
 }
 
 // -------------------------------------------------------------- f32 experts
@@ -1565,16 +1628,13 @@ __device__ __forceinline__ void route_quantise_row(const RouteArgs &A, int row, 
     }
 }
 
-__global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs A) {
-    extern __shared__ __align__(128) unsigned char rt_smem[];
+// Chain role of the routing launches, executed by CTA `cta` of A.n_chain_ctas (block size kRtThreads;
+// for a single token any larger block works too, the extra warps idle).  Returns true in the one CTA that finished
+// last and therefore wrote the plan (never when A.no_plan is set).
+__device__ __forceinline__ bool route_chain_role(const RouteArgs &A, unsigned char *rt_smem, int cta) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if ((int)blockIdx.x >= A.n_chain_ctas) {
-        route_quantise_row(A, blockIdx.x - A.n_chain_ctas, rt_smem);
-        return;
-    }
-    // ---------------- chain role
     const int n_eblk = (A.E + kRtEPB - 1) / kRtEPB;
-    const int eb = blockIdx.x % n_eblk, sb = blockIdx.x / n_eblk;
+    const int eb = cta % n_eblk, sb = cta / n_eblk;
     const int tpc = route_tokens_per_cta(A.M);
     const int e0 = eb * kRtEPB, s0 = sb * tpc;
     const int ne = min(kRtEPB, A.E - e0), ns = min(tpc, A.M - s0);
@@ -1651,7 +1711,7 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
             if (warp == 4 && lane < ne) {
                 prefetch_l2(A.bias + e0 + lane);
                 prefetch_l2(A.experts + e0 + lane);
-                if (blockIdx.x == 0 && lane == 0) prefetch_l2(A.experts + A.E);
+                if (cta == 0 && lane == 0) prefetch_l2(A.experts + A.E);
             }
         } else if (warp == 1 || warp == 3) {
             for (int i = 0; i < nslice; ++i) {
@@ -1859,7 +1919,7 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
         if (*s_last) *A.done_counter = 0u;
     }
     __syncthreads();
-    if (!*s_last || A.no_plan) return;
+    if (!*s_last || A.no_plan) return false;
     __threadfence();
     if (A.small_plan)
         route_plan_small<true>(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts,
@@ -1867,6 +1927,16 @@ __global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs
     else
         route_plan_body(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts, A.plan,
                         rt_smem);
+    return true;
+}
+
+__global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs A) {
+    extern __shared__ __align__(128) unsigned char rt_smem[];
+    if ((int)blockIdx.x >= A.n_chain_ctas) {
+        route_quantise_row(A, blockIdx.x - A.n_chain_ctas, rt_smem);
+        return;
+    }
+    route_chain_role(A, rt_smem, blockIdx.x);
 }
 
 // Speculative routing launch.  Same outputs as route_fused_kernel (int8 copy of x, logits, plan)

@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
     fc.i = blockIdx.x + gridDim.x * warp;
     fc.pass = 0;
     fc.chunk = 0;
-    cursor_seek<RMAX>(fc, P, total, stride);
+    cursor_seek<RMAX>(fc, P, P.slots, total, stride);
     cc = fc;
     uint32_t fq = 0, cq = 0;
 
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
     };
     while (fc.i < total && fq < cq + STAGES) {
         if (lane == 0) issue(fc, fq);
-        cursor_next<RMAX>(fc, P, total, stride);
+        cursor_next<RMAX>(fc, P, P.slots, total, stride);
         ++fq;
     }
 
@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
                 fence_proxy_async();
                 issue(fc, fq);
             }
-            cursor_next<RMAX>(fc, P, total, stride);
+            cursor_next<RMAX>(fc, P, P.slots, total, stride);
             ++fq;
         }
         const uint32_t stage = cq % STAGES;
@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_w4a8_mma_kernel(const Gem
             if (P.mode == 1 && P.comb.col_done != nullptr && cc.pass == cc.npass - 1)
                 ordered_combine_tile(P, cc.tile, lane, n_slots);
         }
-        cursor_next<RMAX>(cc, P, total, stride);
+        cursor_next<RMAX>(cc, P, P.slots, total, stride);
         ++cq;
     }
     if (failed) {

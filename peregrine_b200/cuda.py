@@ -42,7 +42,8 @@ SYMBOLS = [
     # additive entry points
     "coli_cuda_tensor_upload_grouped", "coli_cuda_moe_layer_create", "coli_cuda_moe_layer_set_expert",
     "coli_cuda_moe_layer_free", "coli_cuda_moe_layer_forward_dev", "coli_cuda_moe_layer_forward",
-    "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_set_spec", "coli_cuda_moe_layer_last_pairs",
+    "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_set_spec",
+    "coli_cuda_moe_layer_set_fused", "coli_cuda_moe_layer_decode_timeline", "coli_cuda_moe_layer_last_pairs",
     "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_moe_layer_ep_partial_dev",
     "coli_cuda_moe_layer_ep_combine_dev", "coli_cuda_moe_layer_set_profile", "coli_cuda_moe_layer_profile",
     "coli_cuda_pipe_gemm_noalloc", "coli_cuda_pipe_embed", "coli_cuda_pipe_argmax", "coli_cuda_last_device_error", "coli_cuda_selftest_bounded_wait", "coli_cuda_kernel_launches", "coli_cuda_stream",
@@ -123,6 +124,8 @@ def lib():
         L.coli_cuda_moe_layer_last_routing.argtypes = [vp, i, vp, vp, vp, vp, vp]
         L.coli_cuda_moe_layer_enable_taps.argtypes = [vp, i]
         L.coli_cuda_moe_layer_set_spec.argtypes = [vp, i]
+        L.coli_cuda_moe_layer_set_fused.argtypes = [vp, i]
+        L.coli_cuda_moe_layer_decode_timeline.argtypes = [vp, i, vp, i, vp, vp]
         L.coli_cuda_moe_layer_last_pairs.argtypes = [vp, vp, vp, vp, i]
         L.coli_cuda_moe_layer_read_taps.argtypes = [vp, vp, sz, vp, sz]
         L.coli_cuda_moe_layer_set_ep.argtypes = [vp, i, i]
@@ -490,6 +493,24 @@ class MoeLayer:
         """Speculative routing of decode-sized batches: -1 default, 0 off, 1 on, 2 on with a wrong guess."""
         if lib().coli_cuda_moe_layer_set_spec(self.handle, int(mode)) != 1:
             raise CudaError("cuda moe_layer_set_spec failed")
+
+    def set_fused(self, mode: int):
+        """-1 process default, 0 separate launches, 1 the single-launch decode step (one token)."""
+        if lib().coli_cuda_moe_layer_set_fused(self.handle, mode) != 1:
+            raise CudaError("cuda moe_layer_set_fused failed")
+
+    def decode_timeline(self, enable: bool = True, read: bool = False):
+        """Switches the timeline of the single-launch step on/off; with ``read`` returns
+        ``(stamps [n_ctas, 16] uint64 ns, n_chain)`` of the last such step."""
+        n, nc = C.c_int(0), C.c_int(0)
+        if lib().coli_cuda_moe_layer_decode_timeline(self.handle, int(enable), None, 0, C.byref(n), C.byref(nc)) != 1:
+            raise CudaError("cuda moe_layer_decode_timeline failed")
+        if not read:
+            return None
+        out = np.zeros((n.value, 16), np.uint64)
+        if lib().coli_cuda_moe_layer_decode_timeline(self.handle, int(enable), _ptr(out), n.value, None, None) != 1:
+            raise CudaError("cuda moe_layer_decode_timeline read failed")
+        return out, nc.value
 
     def last_pairs(self, m: int):
         cap = m * (self.k + 1)

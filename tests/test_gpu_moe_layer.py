@@ -170,13 +170,18 @@ def test_speculative_routing_modes_agree_bit_for_bit(dev, m):
     x = synth_tokens(9 + m, m, 512)
     want, idx, w, keff, uni = oracle_layer_forward(layer, x, threads=4, want_routing=True)
     ml = upload_layer(dev, layer)
-    for mode in (0, 1, 2, 1, 0, 2):
-        ml.set_spec(mode)
-        for _ in range(2):
-            got = ml.forward(x)
-            gidx, gw, gkeff, guni = ml.last_routing(m)
-            assert np.array_equal(gidx, idx) and np.array_equal(bits(gw), bits(w)) and list(guni) == list(uni)
-            assert np.array_equal(bits(got), bits(want)), f"mode {mode}"
+    # fused: the single-launch step (one token only) on and off; with it on, mode 2 runs the step a
+    # second time inside the kernel from the exact selection
+    for fused in (1, 0):
+        ml.set_fused(fused)
+        for mode in (0, 1, 2, 1, 0, 2):
+            ml.set_spec(mode)
+            for _ in range(2):
+                got = ml.forward(x)
+                gidx, gw, gkeff, guni = ml.last_routing(m)
+                assert np.array_equal(gidx, idx) and np.array_equal(bits(gw), bits(w)) and list(guni) == list(uni)
+                assert np.array_equal(bits(got), bits(want)), f"mode {mode} fused {fused}"
+    ml.set_fused(-1)
     if m == 2:
         # both tokens equal (every pick of token 1 repeats one of token 0), then partly overlapping picks
         for xx in (np.repeat(x[:1], 2, axis=0), np.stack([x[0], 0.9 * x[0] + 0.1 * x[1]])):
