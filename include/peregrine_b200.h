@@ -220,6 +220,12 @@ int coli_cuda_moe_layer_last_pairs(ColiCudaMoeLayer *layer, int *n_pairs, int *p
 int coli_cuda_moe_layer_read_taps(ColiCudaMoeLayer *layer, int32_t *gateup_taps, size_t gateup_count,
                                   int32_t *down_taps, size_t down_count);
 
+/* Measurement aids (no counterpart in the reference).  int8_peak_probe: tera-ops per second of a
+ * bare tcgen05.mma kind::i8 loop, one CTA per SM (the measured denominator of the prefill roofline).
+ * set_bias: replaces a resident layer's selection bias (host fp32 [E]). */
+double coli_cuda_int8_peak_probe(int device, int iters, int launches);
+int coli_cuda_moe_layer_set_bias(ColiCudaMoeLayer *layer, const float *router_bias);
+
 /* Two device-pointer primitives the decode loop around the FFN needs, in the style of the pipe_* family
  * (no counterpart in cuda/backend_cuda.h; the reference does both on the host):
  * embedding row gather x_dev[s,:] = table_dev[ids_dev[s],:] (fp32 table [V, D]) and greedy
@@ -232,15 +238,32 @@ int coli_cuda_pipe_argmax(int device, int *ids_dev, const float *logits_dev, int
  * hard-codes one device; docs/scale-out-design.md:34-72 sketches an owner map per (layer, expert) and requires
  * cross-device partial sums in fixed order).  Rank r of `world` owns the routed experts
  * [r*ceil(E/world), (r+1)*ceil(E/world)) and only those need to be attached; router and shared expert are
- * replicated.  Every rank runs the partial forward on the WHOLE batch x_all[M, D] (all ranks route
- * identically): it writes the pair rows [M*(k+1), D] of its own experts, and of the shared expert for its home
- * tokens [r*ceil(M/world), ...), and zeros elsewhere.  The caller sums the buffers of all ranks (each row has
- * one non-zero contributor, so the sum is exact in any order) and then combines its home tokens in
- * batch-union order: out[i, :] is token first_token + i. */
+ * replicated; the batch of M tokens is data-parallel, rank r holding tokens [r*M/world, (r+1)*M/world).
+ * A layer step is four phases on the rank's stream, exchanging through blocks of peer-visible memory:
+ * route the home tokens and publish their picks; plan the batch and send each (token, expert) pair's
+ * int8 row to the expert's owner; compute the owned experts and return the un-weighted rows to the
+ * tokens' home ranks; combine the home tokens in batch-union order, shared expert last.  Every
+ * transfer is a store into the peer's block followed by a flag; every wait is bounded and reports
+ * through coli_cuda_last_device_error. */
+typedef struct ColiCudaEp ColiCudaEp;
 int coli_cuda_moe_layer_set_ep(ColiCudaMoeLayer *layer, int rank, int world);
-int coli_cuda_moe_layer_ep_partial_dev(ColiCudaMoeLayer *layer, float *y_pairs_dev, const float *x_all_dev, int M);
-int coli_cuda_moe_layer_ep_combine_dev(ColiCudaMoeLayer *layer, float *out_dev, const float *y_pairs_dev, int M,
-                                       int first_token, int n_tokens);
+/* The exchange block of one rank for batches of M tokens (M a multiple of world) of width D, top-k. */
+int coli_cuda_ep_create(ColiCudaEp **ep, int device, int rank, int world, int M, int D, int k);
+size_t coli_cuda_ep_block_bytes(const ColiCudaEp *ep);
+void *coli_cuda_ep_local_base(const ColiCudaEp *ep);
+/* One process per GPU: export a 64-byte handle, hand it to the other ranks, attach theirs. */
+int coli_cuda_ep_export(ColiCudaEp *ep, void *handle64);
+int coli_cuda_ep_attach(ColiCudaEp *ep, int peer_rank, const void *handle64);
+/* Blocks the process can already address (ranks emulated on one device; devices of one process). */
+int coli_cuda_ep_attach_ptr(ColiCudaEp *ep, int peer_rank, void *base);
+void coli_cuda_ep_free(ColiCudaEp *ep);
+int coli_cuda_moe_layer_ep_route_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep, const float *x_loc_dev);
+int coli_cuda_moe_layer_ep_dispatch_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep);
+int coli_cuda_moe_layer_ep_experts_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep);
+int coli_cuda_moe_layer_ep_finish_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep, float *out_loc_dev);
+/* All four phases: out_loc_dev[M/world, D] = layer(x_loc_dev[M/world, D]) for this rank's home tokens. */
+int coli_cuda_moe_layer_ep_forward_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep, float *out_loc_dev,
+                                       const float *x_loc_dev);
 
 /* Profile mode (in the spirit of COLI_CUDA_PROFILE, cuda/backend_cuda.cu:1068,1174-1207):
  * each forward brackets its seven launches with events, waits for the stream and

@@ -15,6 +15,7 @@
 #include "kernels_tile.cuh"
 #include "kernels_umma.cuh"
 #include "kernels_decode.cuh"
+#include "kernels_ep.cuh"
 #include "w4_host.h"
 
 using namespace pgb;
@@ -984,3 +985,4 @@ __global__ void pipe_add_kernel(float *x, const float *t, size_t n);  // defined
 #include "backend_layer.inc"
 #include "backend_pipe.inc"
 #include "backend_noalloc.inc"
+#include "backend_ep.inc"

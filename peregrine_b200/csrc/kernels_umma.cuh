@@ -478,4 +478,52 @@ __global__ void __launch_bounds__(kUmThreads, 1) ffn_w4a8_umma_kernel(const Gemv
     }
 }
 
+// ---------------------------------------------------------------- int8 tensor peak probe
+// The denominator of the prefill roofline, measured instead of quoted: one CTA per SM issues
+// `iters` back-to-back 128 x 256 x 32 tcgen05.mma kind::i8 (s8 x u8 -> s32) on operands that stay
+// in shared memory, alternating between two 256-column accumulators in tensor memory; nothing else
+// runs.  ops = iters * 2 * 128 * 256 * 32 per CTA.
+constexpr int kPeakABytes = 2 * 128 * 16, kPeakBBytes = 2 * 256 * 16;
+constexpr uint32_t kPeakIdesc = (2u << 4) | (1u << 7) | (0u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+__global__ void __launch_bounds__(128, 1) int8_peak_probe_kernel(int iters, int *err) {
+    __shared__ __align__(128) uint8_t ops[kPeakABytes + kPeakBBytes];
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ uint32_t s_tmem;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    for (int i = tid; i < kPeakABytes + kPeakBBytes; i += blockDim.x)
+        ops[i] = i < kPeakABytes ? (uint8_t)(int8_t)(((i * 37 + 11) % 7) - 3) : (uint8_t)((i * 29 + 5) & 15);
+    const uint32_t b = smem_u32(&bar);
+    if (tid == 0) {
+        mbar_init(b, 1);
+        fence_mbar_init();
+    }
+    fence_proxy_async();  // operands written by threads, read by the tensor core
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tmem_fence_before();
+    __syncthreads();
+    tmem_fence_after();
+    const uint32_t tmem = s_tmem;
+    if (tid == 0) {
+        const uint64_t adesc = umma_desc(smem_u32(ops), 128 * 16, 128);
+        const uint64_t bdesc = umma_desc(smem_u32(ops + kPeakABytes), 256 * 16, 128);
+        for (int i = 0; i < iters; ++i) umma_i8(tmem + (i & 1) * 256, adesc, bdesc, kPeakIdesc, i >= 2 ? 1u : 0u);
+        umma_commit(b);
+        const long long t0 = clock64();
+        while (!mbar_try_wait_park(b, 0u, 20000u))
+            if (clock64() - t0 > 20000000000LL) {
+                report_error(err, kErrBarrierTimeout);
+                break;
+            }
+        tmem_fence_after();
+    }
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+}
+
 }  // namespace pgb

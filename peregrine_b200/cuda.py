@@ -43,9 +43,12 @@ SYMBOLS = [
     "coli_cuda_tensor_upload_grouped", "coli_cuda_moe_layer_create", "coli_cuda_moe_layer_set_expert",
     "coli_cuda_moe_layer_free", "coli_cuda_moe_layer_forward_dev", "coli_cuda_moe_layer_forward",
     "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_set_spec",
-    "coli_cuda_moe_layer_set_fused", "coli_cuda_moe_layer_decode_timeline", "coli_cuda_moe_layer_last_pairs",
-    "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_moe_layer_ep_partial_dev",
-    "coli_cuda_moe_layer_ep_combine_dev", "coli_cuda_moe_layer_set_profile", "coli_cuda_moe_layer_profile",
+    "coli_cuda_moe_layer_set_fused", "coli_cuda_int8_peak_probe", "coli_cuda_moe_layer_set_bias", "coli_cuda_moe_layer_decode_timeline", "coli_cuda_moe_layer_last_pairs",
+    "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_ep_create",
+    "coli_cuda_ep_block_bytes", "coli_cuda_ep_local_base", "coli_cuda_ep_export", "coli_cuda_ep_attach",
+    "coli_cuda_ep_attach_ptr", "coli_cuda_ep_free", "coli_cuda_moe_layer_ep_route_dev",
+    "coli_cuda_moe_layer_ep_dispatch_dev", "coli_cuda_moe_layer_ep_experts_dev", "coli_cuda_moe_layer_ep_finish_dev",
+    "coli_cuda_moe_layer_ep_forward_dev", "coli_cuda_moe_layer_set_profile", "coli_cuda_moe_layer_profile",
     "coli_cuda_pipe_gemm_noalloc", "coli_cuda_pipe_embed", "coli_cuda_pipe_argmax", "coli_cuda_last_device_error", "coli_cuda_selftest_bounded_wait", "coli_cuda_kernel_launches", "coli_cuda_stream",
 ]
 
@@ -125,12 +128,28 @@ def lib():
         L.coli_cuda_moe_layer_enable_taps.argtypes = [vp, i]
         L.coli_cuda_moe_layer_set_spec.argtypes = [vp, i]
         L.coli_cuda_moe_layer_set_fused.argtypes = [vp, i]
+        L.coli_cuda_int8_peak_probe.argtypes = [i, i, i]
+        L.coli_cuda_int8_peak_probe.restype = C.c_double
+        L.coli_cuda_moe_layer_set_bias.argtypes = [vp, vp]
         L.coli_cuda_moe_layer_decode_timeline.argtypes = [vp, i, vp, i, vp, vp]
         L.coli_cuda_moe_layer_last_pairs.argtypes = [vp, vp, vp, vp, i]
         L.coli_cuda_moe_layer_read_taps.argtypes = [vp, vp, sz, vp, sz]
         L.coli_cuda_moe_layer_set_ep.argtypes = [vp, i, i]
-        L.coli_cuda_moe_layer_ep_partial_dev.argtypes = [vp, vp, vp, i]
-        L.coli_cuda_moe_layer_ep_combine_dev.argtypes = [vp, vp, vp, i, i, i]
+        L.coli_cuda_ep_create.argtypes = [vp, i, i, i, i, i, i]
+        L.coli_cuda_ep_block_bytes.argtypes = [vp]
+        L.coli_cuda_ep_block_bytes.restype = sz
+        L.coli_cuda_ep_local_base.argtypes = [vp]
+        L.coli_cuda_ep_local_base.restype = vp
+        L.coli_cuda_ep_export.argtypes = [vp, vp]
+        L.coli_cuda_ep_attach.argtypes = [vp, i, vp]
+        L.coli_cuda_ep_attach_ptr.argtypes = [vp, i, vp]
+        L.coli_cuda_ep_free.argtypes = [vp]
+        L.coli_cuda_ep_free.restype = None
+        L.coli_cuda_moe_layer_ep_route_dev.argtypes = [vp, vp, vp]
+        L.coli_cuda_moe_layer_ep_dispatch_dev.argtypes = [vp, vp]
+        L.coli_cuda_moe_layer_ep_experts_dev.argtypes = [vp, vp]
+        L.coli_cuda_moe_layer_ep_finish_dev.argtypes = [vp, vp, vp]
+        L.coli_cuda_moe_layer_ep_forward_dev.argtypes = [vp, vp, vp, vp]
         L.coli_cuda_moe_layer_set_profile.argtypes = [vp, i]
         L.coli_cuda_moe_layer_profile.argtypes = [vp, vp, vp]
         L.coli_cuda_last_device_error.argtypes = [i]
@@ -210,6 +229,11 @@ def graph_cache_stats() -> GraphCacheStats:
     v = [C.c_uint64(0) for _ in range(4)]
     lib().coli_cuda_graph_cache_stats(*[C.byref(x) for x in v])
     return GraphCacheStats(*[x.value for x in v])
+
+
+def int8_peak_probe(device: int, iters: int = 8192, launches: int = 20) -> float:
+    """Measured int8 tensor throughput (tera-ops/s) of a bare tcgen05 kind::i8 loop, one CTA per SM."""
+    return float(lib().coli_cuda_int8_peak_probe(device, iters, launches))
 
 
 def kernel_launches() -> int:
@@ -494,6 +518,11 @@ class MoeLayer:
         if lib().coli_cuda_moe_layer_set_spec(self.handle, int(mode)) != 1:
             raise CudaError("cuda moe_layer_set_spec failed")
 
+    def set_bias(self, bias):
+        b = _f32(bias)
+        if b.size != self.n_experts or lib().coli_cuda_moe_layer_set_bias(self.handle, _ptr(b)) != 1:
+            raise CudaError("cuda moe_layer_set_bias failed")
+
     def set_fused(self, mode: int):
         """-1 process default, 0 separate launches, 1 the single-launch decode step (one token)."""
         if lib().coli_cuda_moe_layer_set_fused(self.handle, mode) != 1:
@@ -539,16 +568,7 @@ class MoeLayer:
         per = -(-self.n_experts // world)
         return range(min(rank * per, self.n_experts), min((rank + 1) * per, self.n_experts))
 
-    def ep_partial_dev(self, y_pairs_ptr: int, x_all_ptr: int, m: int):
-        if lib().coli_cuda_moe_layer_ep_partial_dev(self.handle, C.c_void_p(y_pairs_ptr), C.c_void_p(x_all_ptr),
-                                                    m) != 1:
-            raise CudaError("cuda moe_layer_ep_partial_dev failed")
-
-    def ep_combine_dev(self, out_ptr: int, y_pairs_ptr: int, m: int, first_token: int, n_tokens: int):
-        if lib().coli_cuda_moe_layer_ep_combine_dev(self.handle, C.c_void_p(out_ptr), C.c_void_p(y_pairs_ptr), m,
-                                                    first_token, n_tokens) != 1:
-            raise CudaError("cuda moe_layer_ep_combine_dev failed")
-
+    # profile mode: names of the seven bracketed stages of a step made of separate launches.
     # "join_repair_or_qrow_h": with speculative routing the wait for the exact plan plus the repair
     # launch; otherwise the separate quantiser of h when the down launch cannot stage it itself
     STAGES = ("qrow_x_unfused", "route", "route_plan_unfused", "gemv_gateup", "join_repair_or_qrow_h", "gemv_down",
