@@ -512,7 +512,66 @@ def extras_one_gpu(torch, cuda, ml, stream, flush, zbias, dev):
         "note": "group-32 format: every 32-element block dot is folded into fp32 on the CUDA cores in reference "
                 "order, which bounds this kernel, not the tensor pipe"}
     del xp, op
+    # configs[4], one-GPU point: the 8-layer subset of the stack, batch 32, 256 greedy steps
+    st = stack_model()
+    ids, secs, ds = stack_decode(torch, cuda, dev, st, stack_ids0())
+    extra["stack_8layer"] = {
+        "value": STACK["batch"] * STACK["steps"] / secs, "unit": UNIT, "seconds": secs, "batch": STACK["batch"],
+        "steps": STACK["steps"], "layers": "3 dense (width 12288) + 5 MoE (256 experts top-8 + shared), hidden 6144, "
+                                           "embedding, final norm, int4 lm_head (vocab 4096), greedy argmax",
+        "distinct_ids": int(len(np.unique(ids))), "timing": "CUDA events around the 256 steps; every step streams "
+        "several GB of expert weights, far more than the L2 holds"}
+    ds.free()
     return extra
+
+
+STACK = dict(n_layers=8, first_dense=3, dense_inter=12288, vocab=4096, batch=EP_BATCH, steps=256, distinct=16)
+
+
+def stack_model():
+    """The 8-layer subset of the synthetic stack of configs[4] (3 dense layers of width 12288, 5 MoE
+    layers as configs[1]); every MoE layer cycles 16 distinct expert blobs on the host, the device
+    holds 256 separate copies per layer."""
+    from peregrine_b200.stack import synth_stack
+
+    c, s = CFG, STACK
+    return synth_stack(seed=9, hidden=c["hidden"], inter=c["inter"], dense_inter=s["dense_inter"],
+                       n_experts=c["n_experts"], k=c["k"], n_layers=s["n_layers"], first_dense=s["first_dense"],
+                       vocab=s["vocab"], gs=c["gs"], distinct_experts=s["distinct"], scale_std=0.02 / 64)
+
+
+def stack_decode(torch, cuda, dev, st, ids0, ep=None, meet=None):
+    """256 greedy steps of the stack for the tokens `ids0`; returns (ids [steps, batch], seconds, stack).
+    `meet` (expert parallel): a host barrier of the ranks; building the stack takes a different time
+    on every rank and the ranks must enter a step within the device-side wait limit of each other."""
+    from peregrine_b200.stack import DeviceStack
+
+    s = STACK
+    ds = DeviceStack(dev, st, len(ids0), s["steps"], ep=ep, repeats="clone")
+    stream = torch.cuda.ExternalStream(cuda.lib().coli_cuda_stream(dev), device=dev)
+    if meet:
+        meet()
+    ds.start(ids0)
+    for t in range(4):  # warm-up steps (overwritten by the timed run)
+        ds.step(t)
+    stream.synchronize()
+    if meet:
+        meet()
+    ds.start(ids0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for t in range(s["steps"]):
+            ds.step(t)
+        e1.record(stream)
+    stream.synchronize()
+    if cuda.last_device_error(dev) != 0:
+        raise RuntimeError("bench: a kernel reported a device-side error during the stack decode")
+    return ds.result(s["steps"]), e0.elapsed_time(e1) * 1e-3, ds
+
+
+def stack_ids0():
+    return (np.arange(STACK["batch"], dtype=np.int32) * 97 + 5) % STACK["vocab"]
 
 
 def run_ep(args, rank: int, local_rank: int, world: int):
@@ -532,6 +591,11 @@ def run_ep(args, rank: int, local_rank: int, world: int):
     c = CFG
     dev = local_rank
     torch.cuda.set_device(dev)
+    # libraries (the collective library's version banner) write to file descriptor 1: keep the real
+    # stdout for the one JSON line and send everything else to stderr
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     dist.init_process_group("nccl", device_id=torch.device("cuda", dev))
     if cuda.init([dev]) < 1:
         raise RuntimeError("bench: the CUDA backend could not initialise its device (no CPU fallback exists)")
@@ -639,6 +703,31 @@ def run_ep(args, rank: int, local_rank: int, world: int):
                    "what": "the same batch through a single-GPU layer holding all 256 experts, same run, rank 0"}
         full.free()
         del xb, ob
+    # ---- the 8-layer stack, expert-parallel: every rank decodes its home tokens for 256 greedy steps;
+    # the ids of all ranks must equal the ids of the same stack on one GPU (rank 0 runs that too)
+    stack = None
+    if m_total == STACK["batch"] and not args.no_extras:
+        st = stack_model()
+        ids0 = stack_ids0()
+        ids_l, secs, ds = stack_decode(torch, cuda, dev, st, ids0[rank * m_local:(rank + 1) * m_local], ep=ws,
+                                       meet=dist.barrier)
+        tsec = torch.tensor([secs], dtype=torch.float64, device=dev)
+        dist.all_reduce(tsec, op=dist.ReduceOp.MAX)
+        ids_t = torch.from_numpy(np.ascontiguousarray(ids_l)).to(dev)
+        parts = [torch.empty_like(ids_t) for _ in range(world)]
+        dist.all_gather(parts, ids_t)
+        ds.free()
+        if rank == 0:
+            ep_ids = torch.cat(parts, 1).cpu().numpy()
+            one_ids, one_secs, ds1 = stack_decode(torch, cuda, dev, st, ids0)
+            ds1.free()
+            stack = {"value": STACK["batch"] * STACK["steps"] / float(tsec.item()), "unit": UNIT,
+                     "seconds": float(tsec.item()), "batch": STACK["batch"], "steps": STACK["steps"], "layers": 8,
+                     "ids_match_one_gpu": bool(np.array_equal(ep_ids, one_ids)),
+                     "base_n1": {"value": STACK["batch"] * STACK["steps"] / one_secs, "seconds": one_secs},
+                     "speedup_vs_n1": one_secs / float(tsec.item())}
+            if not stack["ids_match_one_gpu"]:
+                parity_ok = False
     total_b, _ = algorithmic_bytes(n_union, m_total)
     peak, peak_kind = measured_peaks()
     step_s = total_ms / args.steps * 1e-3
@@ -655,7 +744,7 @@ def run_ep(args, rank: int, local_rank: int, world: int):
         "parity_ok": parity_ok, "base_n1": base_n1,
         "ep_efficiency": (value / (world * base_n1["value"])) if base_n1 else None,
         "ep_speedup_vs_n1": (value / base_n1["value"]) if base_n1 else None,
-        "phase_ms": phase_ms,
+        "phase_ms": phase_ms, "stack_8layer": stack,
         "roofline": {"bound": "hbm", "kernel": "whole layer step (all ranks)", "achieved": total_b / step_s / 1e9,
                      "peak": peak * world, "peak_kind": f"{peak_kind} copy bandwidth x {world} GPUs", "unit": "GB/s",
                      "frac": total_b / step_s / 1e9 / (peak * world), "traffic": None,
@@ -666,7 +755,7 @@ def run_ep(args, rank: int, local_rank: int, world: int):
         "gpu_launches": launches, "clocks": clocks.summary(),
     }
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=json_out, flush=True)
         if parity_ok is False:
             print("bench: the expert-parallel output differs from the single-GPU layer", file=sys.stderr, flush=True)
     # teardown order matters: the process group goes first, then torch's tensors, and the backend

@@ -224,6 +224,9 @@ int coli_cuda_moe_layer_read_taps(ColiCudaMoeLayer *layer, int32_t *gateup_taps,
  * bare tcgen05.mma kind::i8 loop, one CTA per SM (the measured denominator of the prefill roofline).
  * set_bias: replaces a resident layer's selection bias (host fp32 [E]). */
 double coli_cuda_int8_peak_probe(int device, int iters, int launches);
+/* A second resident copy of a tensor made on the device (*out must be NULL): synthetic stacks fill
+ * their layers with distinct memory without repacking every expert on the host. */
+int coli_cuda_tensor_clone(ColiCudaTensor **out, const ColiCudaTensor *src);
 int coli_cuda_moe_layer_set_bias(ColiCudaMoeLayer *layer, const float *router_bias);
 
 /* Two device-pointer primitives the decode loop around the FFN needs, in the style of the pipe_* family
@@ -257,6 +260,11 @@ int coli_cuda_ep_attach(ColiCudaEp *ep, int peer_rank, const void *handle64);
 /* Blocks the process can already address (ranks emulated on one device; devices of one process). */
 int coli_cuda_ep_attach_ptr(ColiCudaEp *ep, int peer_rank, void *base);
 void coli_cuda_ep_free(ColiCudaEp *ep);
+/* The ranks must enter a step within the device-side wait limit (about a second) of each other: after
+ * set-up of uneven length they meet once on the host before the first step.  A wait that runs out
+ * sets the device error word and makes every later wait of that rank give up at once; when all ranks
+ * have drained and met again, each calls this to clear that state. */
+int coli_cuda_ep_reset(ColiCudaEp *ep);
 int coli_cuda_moe_layer_ep_route_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep, const float *x_loc_dev);
 int coli_cuda_moe_layer_ep_dispatch_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep);
 int coli_cuda_moe_layer_ep_experts_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep);

@@ -442,6 +442,34 @@ PGB_EXPORT int coli_cuda_tensor_update(ColiCudaTensor *tensor, const void *weigh
     return tensor_fill(c, tensor, weights, scales);
 }
 
+// A second resident copy of a tensor, made on the device (no host data needed): same format and
+// contents, its own memory.
+PGB_EXPORT int coli_cuda_tensor_clone(ColiCudaTensor **out, const ColiCudaTensor *src) {
+    if (!out || !src || *out) return 0;
+    Ctx *c = find_ctx(src->device);
+    if (!select_ctx(c)) return 0;
+    ColiCudaTensor *t = static_cast<ColiCudaTensor *>(std::calloc(1, sizeof(ColiCudaTensor)));
+    if (!t) return 0;
+    *t = *src;
+    t->data = nullptr;
+    t->row_scales = nullptr;
+    const size_t main_bytes = t->kind ? t->L.total_bytes : t->bytes;
+    const size_t rs_bytes = t->kind == 1 ? (size_t)t->L.ntile * kTileRows * 4 : 0;
+    if (!cuda_ok(cudaMalloc(&t->data, main_bytes), "tensor allocation") ||
+        (rs_bytes && !cuda_ok(cudaMalloc(&t->row_scales, rs_bytes), "scale allocation")) ||
+        !cuda_ok(cudaMemcpy(t->data, src->data, main_bytes, cudaMemcpyDeviceToDevice), "tensor clone") ||
+        (rs_bytes && !cuda_ok(cudaMemcpy(t->row_scales, src->row_scales, rs_bytes, cudaMemcpyDeviceToDevice), "scale clone"))) {
+        if (t->data) cudaFree(t->data);
+        if (t->row_scales) cudaFree(t->row_scales);
+        std::free(t);
+        return 0;
+    }
+    c->tensor_count++;
+    c->tensor_bytes += t->bytes;
+    *out = t;
+    return 1;
+}
+
 PGB_EXPORT void coli_cuda_tensor_free(ColiCudaTensor *tensor) {
     if (!tensor) return;
     Ctx *c = find_ctx(tensor->device);

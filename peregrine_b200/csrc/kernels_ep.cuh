@@ -47,12 +47,22 @@ __device__ __forceinline__ unsigned ep_ld_acquire_sys(const unsigned *p) {
 __device__ __forceinline__ void ep_st_release_sys(unsigned *p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// One thread polls until *p == want; false after ~1 s.
-__device__ __forceinline__ bool ep_wait_flag(const unsigned *p, unsigned want) {
+// One thread polls until *p == want; false after ~1 s.  `failed` is a word of this rank's own block
+// that the first wait to run out sets: every later wait of the rank then gives up at once, so a
+// rank that has lost step with the others (they must enter a step within the wait limit of each
+// other) drains its queued launches in microseconds instead of a second per wait.
+__device__ __forceinline__ bool ep_wait_flag(const unsigned *p, unsigned want, unsigned *failed) {
     const long long t0 = clock64();
     while (ep_ld_acquire_sys(p) != want) {
-        if (clock64() - t0 > kEpWaitCycles) return false;
-        if (clock64() - t0 > 4000) __nanosleep(200);
+        const long long dt = clock64() - t0;
+        if (dt > 4000) {
+            if (*reinterpret_cast<volatile unsigned *>(failed)) return false;
+            if (dt > kEpWaitCycles) {
+                atomicExch(failed, 1u);
+                return false;
+            }
+            __nanosleep(200);
+        }
     }
     return true;
 }
@@ -143,10 +153,23 @@ __global__ void __launch_bounds__(512) ep_select_scatter_kernel(const EpSelectAr
 // ---- 2a. batch-wide plan once every rank's picks are here (one CTA).
 __global__ void __launch_bounds__(256) ep_plan_kernel(const unsigned *ix_flag, int world, unsigned epoch, int M, int E,
                                                       int k, int has_shared, const ExpertDev *__restrict__ experts,
-                                                      RoutePlan plan, int *err) {
+                                                      RoutePlan plan, int *err, unsigned *failed) {
     extern __shared__ __align__(16) unsigned char ep_smem[];
-    if ((int)threadIdx.x < world && !ep_wait_flag(ix_flag + threadIdx.x, epoch)) report_error(err, kErrBarrierTimeout);
-    __syncthreads();
+    int bad = 0;
+    if ((int)threadIdx.x < world && !ep_wait_flag(ix_flag + threadIdx.x, epoch, failed)) {
+        report_error(err, kErrBarrierTimeout);
+        bad = 1;
+    }
+    // without every rank's picks there is nothing to plan (and nothing valid to index with)
+    if (__syncthreads_or(bad)) {
+        if (threadIdx.x == 0) {
+            *plan.n_slots = 0;
+            *plan.n_pairs = 0;
+            *plan.n_union = 0;
+            *plan.shared_pair0 = -1;
+        }
+        return;
+    }
     route_plan_body(nullptr, nullptr, M, E, k, 0, 0.0f, has_shared, experts, plan, ep_smem, true);
 }
 
@@ -159,7 +182,7 @@ struct EpDispatchArgs {
     const float *sx;    // [m_loc]
     int kp, nblk, m_loc, home_lo, k, E, world, has_shared, chunk_major;
     long long pcap;
-    const int *idx, *keff, *tok_pair, *shared_pair0;  // batch-wide plan (local copies)
+    const int *idx, *keff, *tok_pair, *shared_pair0, *n_pairs;  // batch-wide plan (local copies)
     EpPeers peers;
     EpLayout lay;
     unsigned long long set_off;
@@ -170,6 +193,7 @@ struct EpDispatchArgs {
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchArgs A) {
     const int sl = blockIdx.x / (A.k + 1), kk = blockIdx.x % (A.k + 1);
     const int s = A.home_lo + sl;
+    if (*A.n_pairs <= 0) return;  // no plan (a wait ran out): nothing may be indexed
     int p, dst;
     if (kk < A.k) {
         if (kk >= A.keff[s]) return;
@@ -209,12 +233,13 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchArgs A
 // ---- 3a. the owner waits for every row of its experts (slots with rows).  One CTA; thread t takes
 // slots t, t + blockDim, ...
 __global__ void __launch_bounds__(256) ep_wait_rows_kernel(const GemvSlot *__restrict__ slots, const int *n_slots,
-                                                           const unsigned *rx_flag, unsigned epoch, int *err) {
+                                                           const unsigned *rx_flag, unsigned epoch, int *err,
+                                                           unsigned *failed) {
     const int n = *n_slots;
     for (int sl = threadIdx.x; sl < n; sl += blockDim.x) {
         const int r0 = slots[sl].row0, nr = slots[sl].nrows;
         for (int r = 0; r < nr; ++r)
-            if (!ep_wait_flag(rx_flag + r0 + r, epoch)) {
+            if (!ep_wait_flag(rx_flag + r0 + r, epoch, failed)) {
                 report_error(err, kErrBarrierTimeout);
                 return;
             }
@@ -265,7 +290,8 @@ __global__ void __launch_bounds__(288) ep_return_kernel(const EpReturnArgs A) {
 // expert's row is added as out + (w * y) in batch-union order, the shared expert's row last.
 __global__ void __launch_bounds__(256) ep_combine_kernel(const float *__restrict__ y, int D, int k, RoutePlan plan,
                                                          const unsigned *ry_flag, unsigned epoch,
-                                                         float *__restrict__ out, int first_token, int *err) {
+                                                         float *__restrict__ out, int first_token, int *err,
+                                                         unsigned *failed) {
     const int s = first_token + blockIdx.y;
     const int ke = plan.keff[s];
     const int sp0 = *plan.shared_pair0;
@@ -276,9 +302,9 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const float *__restrict
         const int j = threadIdx.x;
         bool ok = true;
         if (j < ke)
-            ok = ep_wait_flag(ry_flag + plan.comb_pair[s * k + j], epoch);
+            ok = ep_wait_flag(ry_flag + plan.comb_pair[s * k + j], epoch, failed);
         else if (sp0 >= 0)
-            ok = ep_wait_flag(ry_flag + sp0 + s, epoch);
+            ok = ep_wait_flag(ry_flag + sp0 + s, epoch, failed);
         if (!ok) {
             report_error(err, kErrBarrierTimeout);
             s_ok = 0;

@@ -43,10 +43,10 @@ SYMBOLS = [
     "coli_cuda_tensor_upload_grouped", "coli_cuda_moe_layer_create", "coli_cuda_moe_layer_set_expert",
     "coli_cuda_moe_layer_free", "coli_cuda_moe_layer_forward_dev", "coli_cuda_moe_layer_forward",
     "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_set_spec",
-    "coli_cuda_moe_layer_set_fused", "coli_cuda_int8_peak_probe", "coli_cuda_moe_layer_set_bias", "coli_cuda_moe_layer_decode_timeline", "coli_cuda_moe_layer_last_pairs",
+    "coli_cuda_moe_layer_set_fused", "coli_cuda_int8_peak_probe", "coli_cuda_tensor_clone", "coli_cuda_moe_layer_set_bias", "coli_cuda_moe_layer_decode_timeline", "coli_cuda_moe_layer_last_pairs",
     "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_ep_create",
     "coli_cuda_ep_block_bytes", "coli_cuda_ep_local_base", "coli_cuda_ep_export", "coli_cuda_ep_attach",
-    "coli_cuda_ep_attach_ptr", "coli_cuda_ep_free", "coli_cuda_moe_layer_ep_route_dev",
+    "coli_cuda_ep_attach_ptr", "coli_cuda_ep_free", "coli_cuda_ep_reset", "coli_cuda_moe_layer_ep_route_dev",
     "coli_cuda_moe_layer_ep_dispatch_dev", "coli_cuda_moe_layer_ep_experts_dev", "coli_cuda_moe_layer_ep_finish_dev",
     "coli_cuda_moe_layer_ep_forward_dev", "coli_cuda_moe_layer_set_profile", "coli_cuda_moe_layer_profile",
     "coli_cuda_pipe_gemm_noalloc", "coli_cuda_pipe_embed", "coli_cuda_pipe_argmax", "coli_cuda_last_device_error", "coli_cuda_selftest_bounded_wait", "coli_cuda_kernel_launches", "coli_cuda_stream",
@@ -128,6 +128,7 @@ def lib():
         L.coli_cuda_moe_layer_enable_taps.argtypes = [vp, i]
         L.coli_cuda_moe_layer_set_spec.argtypes = [vp, i]
         L.coli_cuda_moe_layer_set_fused.argtypes = [vp, i]
+        L.coli_cuda_tensor_clone.argtypes = [vp, vp]
         L.coli_cuda_int8_peak_probe.argtypes = [i, i, i]
         L.coli_cuda_int8_peak_probe.restype = C.c_double
         L.coli_cuda_moe_layer_set_bias.argtypes = [vp, vp]
@@ -143,6 +144,7 @@ def lib():
         L.coli_cuda_ep_export.argtypes = [vp, vp]
         L.coli_cuda_ep_attach.argtypes = [vp, i, vp]
         L.coli_cuda_ep_attach_ptr.argtypes = [vp, i, vp]
+        L.coli_cuda_ep_reset.argtypes = [vp]
         L.coli_cuda_ep_free.argtypes = [vp]
         L.coli_cuda_ep_free.restype = None
         L.coli_cuda_moe_layer_ep_route_dev.argtypes = [vp, vp, vp]
@@ -279,6 +281,13 @@ class Tensor:
             raise CudaError(f"cuda grouped tensor_upload failed (i={i_n}, o={o_n}, gs={gs})")
         return Tensor(h, 4, i_n, o_n, device)
 
+    def clone(self) -> "Tensor":
+        """A second resident copy (device-to-device)."""
+        h = C.c_void_p()
+        if lib().coli_cuda_tensor_clone(C.byref(h), self.handle) != 1:
+            raise CudaError("cuda tensor_clone failed")
+        return Tensor(h, self.fmt, self.i_n, self.o_n, self.device)
+
     def update(self, weights, scales):
         w = np.ascontiguousarray(weights)
         s = None if scales is None else _f32(scales)
@@ -337,6 +346,9 @@ class GpuExpert:
         u = Tensor.upload_grouped(device, up[0], up[1], hidden, inter, gs)
         d = Tensor.upload_grouped(device, down[0], down[1], inter, hidden, gs)
         return GpuExpert(g, u, d)
+
+    def clone(self) -> "GpuExpert":
+        return GpuExpert(self.gate.clone(), self.up.clone(), self.down.clone())
 
     def free(self):
         for t in (self.gate, self.up, self.down):

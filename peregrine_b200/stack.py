@@ -32,7 +32,12 @@ class SynthStack:
 
 
 def synth_stack(seed: int, hidden: int, inter: int, dense_inter: int, n_experts: int, k: int, n_layers: int,
-                first_dense: int, vocab: int, gs: int = 32, distinct_experts: int | None = None) -> SynthStack:
+                first_dense: int, vocab: int, gs: int = 32, distinct_experts: int | None = None,
+                scale_std: float = 0.02) -> SynthStack:
+    """``scale_std``: standard deviation of the weight scales.  At hidden sizes in the thousands the
+    default 0.02 makes every FFN output dwarf the residual stream and greedy decoding collapses onto
+    one token whatever the input; wide stacks pass a smaller value so that the ids keep depending on
+    the tokens (the arithmetic under test is the same)."""
     rng = np.random.default_rng(seed)
     embed = rng.standard_normal((vocab, hidden)).astype(np.float32)
     norms = [(1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32) for _ in range(n_layers)]
@@ -41,10 +46,10 @@ def synth_stack(seed: int, hidden: int, inter: int, dense_inter: int, n_experts:
     layers = []
     for li in range(n_layers):
         if li < first_dense:
-            layers.append(synth_expert(rng, hidden, dense_inter, gs))
+            layers.append(synth_expert(rng, hidden, dense_inter, gs, scale_std))
         else:
             layers.append(synth_layer(seed * 1000 + li, hidden, inter, n_experts, k, gs, shared=True,
-                                      distinct_experts=distinct_experts))
+                                      distinct_experts=distinct_experts, scale_std=scale_std))
     return SynthStack(hidden, vocab, 1e-5, embed, norms, final_norm, lm_head, layers)
 
 
@@ -73,11 +78,15 @@ class _DevBuf:
 
 
 class DeviceStack:
-    """The stack resident on one device; ``decode`` runs greedy steps without host round trips."""
+    """The stack resident on one device; ``decode`` runs greedy steps without host round trips.
 
-    def __init__(self, device: int, st: SynthStack, batch: int, max_steps: int):
+    Expert parallel (``ep`` = an ``EpWorkspace`` connected to the other ranks): this rank holds the
+    routed experts it owns of every MoE layer and decodes ``batch`` = its home tokens; everything
+    outside the MoE layers is per token, so only those layers exchange."""
+
+    def __init__(self, device: int, st: SynthStack, batch: int, max_steps: int, ep=None, repeats: str = "upload"):
         L = cuda.lib()
-        self.device, self.st, self.batch, self.max_steps = device, st, batch, max_steps
+        self.device, self.st, self.batch, self.max_steps, self.ep = device, st, batch, max_steps, ep
         self.embed = _DevBuf(device, st.embed)
         self.norms = [_DevBuf(device, w) for w in st.norms]
         self.final_norm = _DevBuf(device, st.final_norm)
@@ -86,7 +95,13 @@ class DeviceStack:
         self.layers = []
         for layer in st.layers:
             if isinstance(layer, SynthLayer):
-                self.layers.append(upload_layer(device, layer))
+                if ep is not None:
+                    from .ep import owned_range
+
+                    self.layers.append(upload_layer(device, layer, owned_range(layer.n_experts, ep.rank, ep.world),
+                                                    ep.rank, ep.world, repeats))
+                else:
+                    self.layers.append(upload_layer(device, layer, repeats=repeats))
             else:
                 self.layers.append(upload_expert(device, layer, st.hidden, layer.gate.o_n))
         d, b = st.hidden, batch
@@ -115,7 +130,11 @@ class DeviceStack:
             self._ok(L.coli_cuda_pipe_rmsnorm(dev, vp(self.nrm.ptr), vp(self.x.ptr), vp(self.norms[li].ptr), b, d,
                                               C.c_float(st.eps)), "rmsnorm")
             if isinstance(layer, cuda.MoeLayer):
-                layer.forward_dev(self.ffn.ptr, self.nrm.ptr, b)
+                if self.ep is not None:
+                    self._ok(L.coli_cuda_moe_layer_ep_forward_dev(layer.handle, self.ep.handle, vp(self.ffn.ptr),
+                                                                  vp(self.nrm.ptr)), "expert-parallel layer")
+                else:
+                    layer.forward_dev(self.ffn.ptr, self.nrm.ptr, b)
             else:
                 inter = layer.gate.o_n
                 self._ok(L.coli_cuda_pipe_gemm(layer.gate.handle, vp(self.g.ptr), vp(self.nrm.ptr), b), "gate")
@@ -128,16 +147,22 @@ class DeviceStack:
         self._ok(L.coli_cuda_pipe_gemm(self.lm_head.handle, vp(self.logits.ptr), vp(self.nrm.ptr), b), "lm_head")
         self._ok(L.coli_cuda_pipe_argmax(dev, ids_out, vp(self.logits.ptr), b, st.vocab), "argmax")
 
+    def start(self, ids0: np.ndarray):
+        ids0 = np.ascontiguousarray(ids0, np.int32)
+        self._ok(self._L.coli_cuda_pipe_upload(self.device, C.c_void_p(self.ids.ptr), ids0.ctypes.data, ids0.nbytes),
+                 "ids upload")
+
+    def result(self, steps: int) -> np.ndarray:
+        return self.ids.download((steps + 1, self.batch), np.int32)[1:]
+
     def decode(self, ids0: np.ndarray, steps: int) -> np.ndarray:
         """Greedy decode: returns int32 ids [steps, batch] (the tokens picked at each step)."""
         if steps > self.max_steps:
             raise ValueError("more steps than the id buffer holds")
-        ids0 = np.ascontiguousarray(ids0, np.int32)
-        self._ok(self._L.coli_cuda_pipe_upload(self.device, C.c_void_p(self.ids.ptr), ids0.ctypes.data, ids0.nbytes),
-                 "ids upload")
+        self.start(ids0)
         for t in range(steps):
             self.step(t)
-        return self.ids.download((steps + 1, self.batch), np.int32)[1:]
+        return self.result(steps)
 
     def free(self):
         for l in self.layers:

@@ -44,20 +44,20 @@ class SynthLayer:
     shared: SynthExpert | None = None
 
 
-def synth_matrix(rng: np.random.Generator, o_n: int, i_n: int, gs: int) -> SynthMatrix:
+def synth_matrix(rng: np.random.Generator, o_n: int, i_n: int, gs: int, scale_std: float = 0.02) -> SynthMatrix:
     rb = (i_n + 1) // 2
     q = rng.integers(0, 256, size=o_n * rb, dtype=np.uint8)
     if i_n % 2:
         q.reshape(o_n, rb)[:, -1] &= 0x0F
     ng = -(-i_n // gs) if gs else 1
-    scale = np.abs(rng.standard_normal(o_n * ng).astype(np.float32) * np.float32(0.02))
-    scale = np.maximum(scale, np.float32(1e-6)).astype(np.float32)
+    scale = np.abs(rng.standard_normal(o_n * ng).astype(np.float32) * np.float32(scale_std))
+    scale = np.maximum(scale, np.float32(scale_std * 5e-5)).astype(np.float32)
     return SynthMatrix(q, scale, i_n, o_n, gs)
 
 
-def synth_expert(rng, hidden: int, inter: int, gs: int) -> SynthExpert:
-    return SynthExpert(synth_matrix(rng, inter, hidden, gs), synth_matrix(rng, inter, hidden, gs),
-                       synth_matrix(rng, hidden, inter, gs))
+def synth_expert(rng, hidden: int, inter: int, gs: int, scale_std: float = 0.02) -> SynthExpert:
+    return SynthExpert(synth_matrix(rng, inter, hidden, gs, scale_std), synth_matrix(rng, inter, hidden, gs, scale_std),
+                       synth_matrix(rng, hidden, inter, gs, scale_std))
 
 
 def zipf_bias(rng, n_experts: int, s: float = 1.1, strength: float = 0.35) -> np.ndarray:
@@ -73,7 +73,7 @@ def zipf_bias(rng, n_experts: int, s: float = 1.1, strength: float = 0.35) -> np
 
 def synth_layer(seed: int, hidden: int, inter: int, n_experts: int, k: int, gs: int = 32, shared: bool = True,
                 norm_topk: bool = True, routed_scale: float = 2.5, zipf: bool = False,
-                distinct_experts: int | None = None) -> SynthLayer:
+                distinct_experts: int | None = None, scale_std: float = 0.02) -> SynthLayer:
     """``distinct_experts`` < n_experts reuses weight blobs cyclically (host RAM
     saver for CPU-side tests only; a device upload still makes n_experts copies)."""
     rng = np.random.default_rng(seed)
@@ -81,10 +81,10 @@ def synth_layer(seed: int, hidden: int, inter: int, n_experts: int, k: int, gs: 
     bias = zipf_bias(rng, n_experts) if zipf else np.zeros(n_experts, np.float32)
     layer = SynthLayer(hidden, inter, n_experts, k, gs, norm_topk, routed_scale, router_w, bias)
     nd = n_experts if distinct_experts is None else min(distinct_experts, n_experts)
-    blobs = [synth_expert(rng, hidden, inter, gs) for _ in range(nd)]
+    blobs = [synth_expert(rng, hidden, inter, gs, scale_std) for _ in range(nd)]
     layer.experts = [blobs[e % nd] for e in range(n_experts)]
     if shared:
-        layer.shared = synth_expert(rng, hidden, inter, gs)
+        layer.shared = synth_expert(rng, hidden, inter, gs, scale_std)
     return layer
 
 

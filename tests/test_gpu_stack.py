@@ -28,6 +28,24 @@ def test_greedy_ids_identical_over_256_steps(dev):
     ds.free()
 
 
+def test_greedy_ids_at_the_benchmark_layer_shape(dev):
+    """The stack at the real layer shapes of the full-stack benchmark config: hidden 6144, one dense layer
+    of width 12288, two MoE layers with 256 experts (top-8 + shared, width 2048), batch 4, 16 greedy
+    steps; ids identical to the oracle's.  The experts reuse four host blobs (the oracle's memory and
+    the upload time stay small); every expert id is attached and routable."""
+    st = synth_stack(seed=5, hidden=6144, inter=2048, dense_inter=12288, n_experts=256, k=8, n_layers=3,
+                     first_dense=1, vocab=4096, distinct_experts=4, scale_std=0.02 / 64)
+    batch, steps = 4, 16
+    ids0 = np.array([3, 1000, 2222, 4000], np.int32)
+    ds = DeviceStack(dev, st, batch, steps, repeats="share")
+    got = ds.decode(ids0, steps)
+    want = oracle_stack_decode(st, ids0, steps, threads=8)
+    assert np.array_equal(got, want)
+    assert len(np.unique(got)) > 4
+    assert cuda.last_device_error(dev) == 0
+    ds.free()
+
+
 def test_argmax_rules_on_device(dev):
     import ctypes as C
 
