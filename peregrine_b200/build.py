@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcoli_cuda_backend.so")
 
 SOURCES = ["backend.cu", "w4_host.cpp"]
-DEPS = ["kernels.cuh", "kernels_mma.cuh", "kernels_tile.cuh", "kernels_umma.cuh", "kernels_decode.cuh", "kernels_ep.cuh", "backend_ep.inc", "w4_layout.h", "w4_host.h", "backend_layer.inc", "backend_pipe.inc", "backend_noalloc.inc",
+DEPS = ["kernels.cuh", "kernels_mma.cuh", "kernels_tile.cuh", "kernels_umma.cuh", "kernels_decode.cuh", "kernels_block.cuh", "kernels_ep.cuh", "backend_ep.inc", "w4_layout.h", "w4_host.h", "backend_layer.inc", "backend_pipe.inc", "backend_noalloc.inc",
         os.path.join("..", "..", "include", "peregrine_b200.h")]
 
 NVCC_FLAGS = [

@@ -14,6 +14,7 @@
 #include "kernels_mma.cuh"
 #include "kernels_tile.cuh"
 #include "kernels_umma.cuh"
+#include "kernels_block.cuh"
 #include "kernels_decode.cuh"
 #include "kernels_ep.cuh"
 #include "w4_host.h"
@@ -551,6 +552,31 @@ static int mma_launch_r(Ctx *c, const GemvParams &P, bool grouped, int bpg) {
     return fail("w4a8 mma gemv: unsupported group size");
 }
 
+// ---- batched-decode variant: more than 8 rows in some slot; the CTA's warps share the activation rows
+template <bool GROUPED, int BPG>
+static int block_launch_t(Ctx *c, const GemvParams &P) {
+    auto kfn = gemv_w4a8_block_kernel<GROUPED, BPG>;
+    if (!ensure_smem(c, kfn, (size_t)kBlkSmemBytes, "block gemv shared-memory opt-in")) return 0;
+    return launch(kfn, dim3(c->sms), dim3(kBlkThreads), (size_t)kBlkSmemBytes, c->stream, "w4a8 block gemv launch", P);
+}
+static int block_launch(Ctx *c, const GemvParams &P, bool grouped, int bpg) {
+    if (!grouped) return block_launch_t<false, 1>(c, P);
+    switch (bpg) {
+        case 1: return block_launch_t<true, 1>(c, P);
+        case 2: return block_launch_t<true, 2>(c, P);
+        case 4: return block_launch_t<true, 4>(c, P);
+        case 8: return block_launch_t<true, 8>(c, P);
+    }
+    return fail("w4a8 block gemv: unsupported group size");
+}
+static int block_min_rows() {
+    static const int v = [] {
+        const char *e = std::getenv("PEREGRINE_B200_BLOCK_MIN_ROWS");
+        return e ? std::atoi(e) : 9;
+    }();
+    return v;
+}
+
 // Rows per expert beyond which the tensor-core kernel (and the chunk-major activation layout) is used.
 static bool gemv_uses_mma(int max_rows) { return max_rows > 2; }
 // Bytes of the quantised activations of `rows` rows in the layout the kernel for `max_rows` reads.
@@ -635,6 +661,8 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
     if (gemv_uses_mma(max_rows)) {
         if (want_quant_stage) return fail("w4a8 gemv: quantising stage is not available beyond 2 rows per expert");
         if (P.pcap <= 0) return fail("w4a8 gemv: the tensor-core kernel needs chunk-major activations");
+        // experts with many rows: the warps of a CTA share the rows (no inspection taps on that path)
+        if (!P.tap && max_rows >= block_min_rows()) return block_launch(c, P, grouped, L.bpg);
         if (max_rows <= 8) return mma_launch_r<1>(c, P, grouped, L.bpg);
         return mma_launch_r<2>(c, P, grouped, L.bpg);
     }
