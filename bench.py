@@ -37,7 +37,8 @@ EP_BATCH = 32            # configs[4]: decode batch of the expert-parallel runs
 ROUTER_SEED, SHARED_SEED, EXPERT_SEED0 = 1234, 4999, 5000
 # DRAM traffic of one single-launch decode step from a profiler capture of that kernel
 # (dram__bytes_read.sum + dram__bytes_write.sum): a recorded constant, not measured by this run.
-RECORDED_STEP_TRAFFIC = {"bytes": None, "source": "profiles/decode_step_kernel_m1.md"}
+RECORDED_STEP_TRAFFIC = {"bytes": 225.1e6, "source": "profiles/decode_step_kernel_m1.md (captured at 64 resident "
+                         "experts: 220.4 MB; + 4.72 MB of router rows at 256)"}
 
 
 def ep_workload_text(m_total: int, world: int) -> str:
@@ -396,18 +397,23 @@ def run_ours(args, rank: int, local_rank: int, world: int):
 
     # ---- end to end through the host-pointer call (H2D of x and D2H of the result inside)
     e2e_steps = min(args.steps, 300)
+    out_host = np.empty((m, c["hidden"]), np.float32)
     for i in range(3):
-        ml.forward(xs_host[i % N_TOKENS])
+        ml.forward(xs_host[i % N_TOKENS], out_host)
+    ml.host_times(reset=True)
     e2e_t = 0.0
     for i in range(e2e_steps):
         with torch.cuda.stream(stream):
             flush()
         stream.synchronize()
         t0 = time.perf_counter()
-        ml.forward(xs_host[i % N_TOKENS])
+        ml.forward(xs_host[i % N_TOKENS], out_host)
         e2e_t += time.perf_counter() - t0
+    host_us, _ = ml.host_times(reset=True)
     e2e = {"value": m * e2e_steps / e2e_t, "unit": UNIT, "h2d_bytes_per_step": m * c["hidden"] * 4,
            "d2h_bytes_per_step": m * c["hidden"] * 4, "steps": e2e_steps,
+           "us_per_call": e2e_t / e2e_steps * 1e6,
+           "host_us_inside_call": {k: round(v, 2) for k, v in host_us.items()},
            "call": "coli_cuda_moe_layer_forward (host x in, host out back, blocking)"}
 
     line = {

@@ -277,6 +277,9 @@ int coli_cuda_moe_layer_ep_forward_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep, 
  * each forward brackets its seven launches with events, waits for the stream and
  * accumulates per-stage device milliseconds: quantise x, router logits, routing plan,
  * gate/up GEMV, quantise h, down GEMV, combine.  Switching resets the accumulators. */
+/* Host-side microseconds of coli_cuda_moe_layer_forward since the last reset, by part: staging copy of
+ * x, enqueueing the upload, enqueueing the launches, waiting for the device, copying the result out. */
+int coli_cuda_moe_layer_host_times(ColiCudaMoeLayer *layer, double *us5, uint64_t *calls, int reset);
 int coli_cuda_moe_layer_set_profile(ColiCudaMoeLayer *layer, int enable);
 int coli_cuda_moe_layer_profile(ColiCudaMoeLayer *layer, double *stage_ms7, uint64_t *calls);
 
@@ -289,8 +292,8 @@ int coli_cuda_moe_layer_profile(ColiCudaMoeLayer *layer, double *stage_ms7, uint
  * runs with VRAM fully committed to experts, or where a device-wide synchronising call is
  * not allowed.  Requests whose scratch exceeds 1 MiB (about S*I*1.2 bytes; S <= 143 at
  * I = 6144) are refused with a message.  The first call on a device resolves the array's
- * address and should come before any stream capture; all calls on a device share the array,
- * so calls that overlap on the GPU race. */
+ * address and configures the kernels; all calls on a device share the array, so calls that
+ * overlap on the GPU race. */
 int coli_cuda_pipe_gemm_noalloc(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S);
 
 /* Device error word of a context: 0 when no kernel reported a problem since the

@@ -662,7 +662,7 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
         if (want_quant_stage) return fail("w4a8 gemv: quantising stage is not available beyond 2 rows per expert");
         if (P.pcap <= 0) return fail("w4a8 gemv: the tensor-core kernel needs chunk-major activations");
         // experts with many rows: the warps of a CTA share the rows (no inspection taps on that path)
-        if (!P.tap && max_rows >= block_min_rows()) return block_launch(c, P, grouped, L.bpg);
+        if (!P.tap && P.comb.col_done == nullptr && max_rows >= block_min_rows()) return block_launch(c, P, grouped, L.bpg);
         if (max_rows <= 8) return mma_launch_r<1>(c, P, grouped, L.bpg);
         return mma_launch_r<2>(c, P, grouped, L.bpg);
     }
@@ -677,8 +677,8 @@ static int gemv_run(Ctx *c, GemvParams P, const W4Layout &L, int mode, int max_r
 
 // Loads and configures every kernel a single-matrix product (down-style launch, no taps, no
 // quantising stage) of this weight format can reach, whatever the row count: the dp4a kernel for 1
-// and 2 rows with and without staged activations, the tensor-core kernel for 8 and 16 rows per
-// pass, the quantiser and the slot writer.  After this no later call on the device meets a first-use
+// and 2 rows with and without staged activations, the tensor-core kernels for 8 and 16 rows per
+// pass and for shared rows, the quantiser and the slot writer.  After this no later call on the device meets a first-use
 // module load or a shared-memory opt-in for these kernels.
 template <bool GROUPED, int BPG>
 static int gemm_prepare_t(Ctx *c) {
@@ -694,6 +694,7 @@ static int gemm_prepare_t(Ctx *c) {
     touch(gemv_w4a8_kernel<2, GROUPED, BPG, 1, false>, c->smem_optin, "gemv preparation");
     touch(gemv_w4a8_mma_kernel<1, GROUPED, BPG, false>, (size_t)mma_ring_bytes(1) + kMmaBarBytes, "mma gemv preparation");
     touch(gemv_w4a8_mma_kernel<2, GROUPED, BPG, false>, (size_t)mma_ring_bytes(2) + kMmaBarBytes, "mma gemv preparation");
+    touch(gemv_w4a8_block_kernel<GROUPED, BPG>, (size_t)kBlkSmemBytes, "block gemv preparation");
     touch(qrow_i8_kernel, 0, "quantiser preparation");
     touch(write_slot_kernel, 0, "slot writer preparation");
     return ok;

@@ -1295,9 +1295,11 @@ constexpr int kRtThreads = 288;  // 9 warps
 constexpr int kRtRingBytes = 160 * 1024;   // the ring uses as many stages as fit here (at most 16)
 constexpr int kRtBarOffset = kRtRingBytes; // barriers and flags follow the ring
 // slice length along D: long slices for a single token (fewer hand-overs on the critical chain)
-// tokens per chain CTA: 32 (one chain per thread) up to 32 tokens, above that 64 (two independent
-// chains per thread fill the issue slots a single dependent chain leaves empty)
-__host__ __device__ inline int route_tokens_per_cta(int M) { return M > kRtMT ? 2 * kRtMT : kRtMT; }
+// tokens per chain CTA: 16 up to 32 tokens (one chain per thread, 128 chain threads: one warp per
+// scheduler, so nothing competes with a chain for its issue slots: a chain is a string of dependent
+// adds, and two chain warps on one scheduler took more than twice as long as one), above that 64
+// (two independent chains per thread)
+__host__ __device__ inline int route_tokens_per_cta(int M) { return M > kRtMT ? 2 * kRtMT : kRtMT / 2; }
 __host__ __device__ inline int route_slice(int M) { return M == 1 ? 512 : 256; }
 // floats per operand row inside a stage: 16-byte skew so the 8 router rows land on distinct banks
 __host__ __device__ inline int route_row_floats(int M) { return route_slice(M) + 4; }
@@ -1646,7 +1648,9 @@ __device__ __forceinline__ bool route_chain_role(const RouteArgs &A, unsigned ch
     if (tid == 0) {
         for (int s = 0; s < kRtStages; ++s) {
             mbar_init(full_u32 + s * 8, 1);
-            mbar_init(empty_u32 + s * 8, A.M == 1 ? 1 : 8);  // decode: only the chain warp releases a stage
+            // a stage is released by the warps that run chains: one (decode), those that hold a token of
+            // the block (batches up to 32 tokens), all eight (above)
+            mbar_init(empty_u32 + s * 8, A.M == 1 ? 1 : (A.M > kRtMT ? 8 : (ns * kRtEPB + 31) / 32));
             mbar_init(empty_u32 + kRtMaxStages * 8 + s * 8, 2);  // products ready: warps 1 and 3
         }
         fence_mbar_init();
@@ -1841,7 +1845,7 @@ __device__ __forceinline__ bool route_chain_role(const RouteArgs &A, unsigned ch
             if (sl < ns) A.logits[(long long)(s0 + sl) * A.E + e0 + el] = acc0;
             if (sl + 32 < ns) A.logits[(long long)(s0 + sl + 32) * A.E + e0 + el] = acc1;
         }
-    } else {
+    } else if (warp < (ns * kRtEPB + 31) / 32) {
         const int el = tid & 7, sl = tid >> 3;
         const bool chain = (el < ne) && (sl < ns);
         float acc = 0.0f;
@@ -1857,47 +1861,58 @@ __device__ __forceinline__ bool route_chain_role(const RouteArgs &A, unsigned ch
                 const float *xr =
                     reinterpret_cast<const float *>(rt_smem + st * kRtStageBytes) + (xrow0 + sl) * kRtRowFloats;
                 const int dlen = min(kRtSL, A.D - i * kRtSL);
-                if (dlen == kRtSL) {
-                    // three-stage software pipeline written out in source order: the adds of step i are
-                    // interleaved with the multiplies of step i+1 and the loads of step i+2, so the
-                    // independent work fills the issue slots the dependent adds leave free
-                    float4 wv[4], xv[4];
-                    float p[16];
+                if (dlen == kRtSL && (kRtSL & 31) == 0) {
+                    // Software pipeline over two register sets (a, b), 16 elements each, written out in
+                    // source order: while the 16 dependent adds of one set run, the products of the other
+                    // are formed and the operands after those are loaded, so the independent work fills
+                    // the issue slots the adds leave free and no value is ever copied between registers.
+                    float4 wa[4], xa[4], wb[4], xb[4];
+                    float pa[16], pb[16];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        wv[j] = *reinterpret_cast<const float4 *>(wr + 4 * j);
-                        xv[j] = *reinterpret_cast<const float4 *>(xr + 4 * j);
+                        wa[j] = *reinterpret_cast<const float4 *>(wr + 4 * j);
+                        xa[j] = *reinterpret_cast<const float4 *>(xr + 4 * j);
+                        wb[j] = *reinterpret_cast<const float4 *>(wr + 16 + 4 * j);
+                        xb[j] = *reinterpret_cast<const float4 *>(xr + 16 + 4 * j);
                     }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        p[4 * j + 0] = __fmul_rn(xv[j].x, wv[j].x);
-                        p[4 * j + 1] = __fmul_rn(xv[j].y, wv[j].y);
-                        p[4 * j + 2] = __fmul_rn(xv[j].z, wv[j].z);
-                        p[4 * j + 3] = __fmul_rn(xv[j].w, wv[j].w);
-                        wv[j] = *reinterpret_cast<const float4 *>(wr + 16 + 4 * j);
-                        xv[j] = *reinterpret_cast<const float4 *>(xr + 16 + 4 * j);
+                        pa[4 * j + 0] = __fmul_rn(xa[j].x, wa[j].x);
+                        pa[4 * j + 1] = __fmul_rn(xa[j].y, wa[j].y);
+                        pa[4 * j + 2] = __fmul_rn(xa[j].z, wa[j].z);
+                        pa[4 * j + 3] = __fmul_rn(xa[j].w, wa[j].w);
                     }
 #pragma unroll 1
-                    for (int d = 0; d < kRtSL; d += 16) {
-                        float pn[16];
-                        // loads two steps ahead stay inside the padded row of this stage or read the
-                        // next row of the stage; values past the slice are never added
-                        const int dl = min(d + 32, kRtSL - 16);
+                    for (int d = 0; d < kRtSL; d += 32) {
+                        // loads past the slice stay inside the padded row of this stage or read the next
+                        // row of the stage; values past the slice are never added
+                        const int l0 = min(d + 32, kRtSL - 16), l1 = min(d + 48, kRtSL - 16);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            acc = __fadd_rn(acc, p[4 * j + 0]);
-                            pn[4 * j + 0] = __fmul_rn(xv[j].x, wv[j].x);
-                            acc = __fadd_rn(acc, p[4 * j + 1]);
-                            pn[4 * j + 1] = __fmul_rn(xv[j].y, wv[j].y);
-                            acc = __fadd_rn(acc, p[4 * j + 2]);
-                            pn[4 * j + 2] = __fmul_rn(xv[j].z, wv[j].z);
-                            acc = __fadd_rn(acc, p[4 * j + 3]);
-                            pn[4 * j + 3] = __fmul_rn(xv[j].w, wv[j].w);
-                            wv[j] = *reinterpret_cast<const float4 *>(wr + dl + 4 * j);
-                            xv[j] = *reinterpret_cast<const float4 *>(xr + dl + 4 * j);
+                            acc = __fadd_rn(acc, pa[4 * j + 0]);
+                            pb[4 * j + 0] = __fmul_rn(xb[j].x, wb[j].x);
+                            acc = __fadd_rn(acc, pa[4 * j + 1]);
+                            pb[4 * j + 1] = __fmul_rn(xb[j].y, wb[j].y);
+                            acc = __fadd_rn(acc, pa[4 * j + 2]);
+                            pb[4 * j + 2] = __fmul_rn(xb[j].z, wb[j].z);
+                            acc = __fadd_rn(acc, pa[4 * j + 3]);
+                            pb[4 * j + 3] = __fmul_rn(xb[j].w, wb[j].w);
+                            wa[j] = *reinterpret_cast<const float4 *>(wr + l0 + 4 * j);
+                            xa[j] = *reinterpret_cast<const float4 *>(xr + l0 + 4 * j);
                         }
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) p[j] = pn[j];
+                        for (int j = 0; j < 4; ++j) {
+                            acc = __fadd_rn(acc, pb[4 * j + 0]);
+                            pa[4 * j + 0] = __fmul_rn(xa[j].x, wa[j].x);
+                            acc = __fadd_rn(acc, pb[4 * j + 1]);
+                            pa[4 * j + 1] = __fmul_rn(xa[j].y, wa[j].y);
+                            acc = __fadd_rn(acc, pb[4 * j + 2]);
+                            pa[4 * j + 2] = __fmul_rn(xa[j].z, wa[j].z);
+                            acc = __fadd_rn(acc, pb[4 * j + 3]);
+                            pa[4 * j + 3] = __fmul_rn(xa[j].w, wa[j].w);
+                            wb[j] = *reinterpret_cast<const float4 *>(wr + l1 + 4 * j);
+                            xb[j] = *reinterpret_cast<const float4 *>(xr + l1 + 4 * j);
+                        }
                     }
                 } else {
                     for (int d = 0; d < dlen; ++d) acc = __fadd_rn(acc, __fmul_rn(xr[d], wr[d]));
@@ -1930,7 +1945,7 @@ __device__ __forceinline__ bool route_chain_role(const RouteArgs &A, unsigned ch
     return true;
 }
 
-__global__ void __launch_bounds__(kRtThreads) route_fused_kernel(const RouteArgs A) {
+__global__ void __launch_bounds__(kRtThreads, 1) route_fused_kernel(const RouteArgs A) {
     extern __shared__ __align__(128) unsigned char rt_smem[];
     if ((int)blockIdx.x >= A.n_chain_ctas) {
         route_quantise_row(A, blockIdx.x - A.n_chain_ctas, rt_smem);

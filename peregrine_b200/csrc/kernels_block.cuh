@@ -6,44 +6,61 @@
 // as the chunk's packed weights (5 KB for a tile pair), the traffic from L2 into the SM doubles and
 // an expert with more than 16 rows is streamed once per 16 rows.  Here a work item is (expert, block
 // of 8 tile pairs), run in passes of up to 32 rows: a producer warp fills a CTA-wide ring stage by stage with
-// the 8 warps' weight chunks, ONE copy of the pass's activation rows of that chunk and their block
-// sums; each consumer warp multiplies its own tile pair with all rows of the pass (m16n8k32 int8
-// MMAs, 1 to 4 column groups of 8 rows, chosen per item) and folds the group dots into fp32 in the
-// reference's order (crates/peregrine-kernels/src/idot.rs:98-110, matmul.rs:75-106): the same
-// arithmetic, accumulator presets and packed fold as gemv_w4a8_mma_kernel.  An expert's weights are
-// fetched once per 32 rows, the activation rows once per CTA instead of once per warp.
+// the 8 pairs' weight chunks, ONE copy of the pass's activation rows of that chunk and their block
+// sums; 16 consumer warps take one 16-row tile each (warp 2p + h: half h of pair p), multiply it with
+// all rows of the pass (m16n8k32 int8 MMAs, 1 to 4 column groups of 8 rows, chosen per item) and fold
+// the group dots into fp32 in the reference's order (crates/peregrine-kernels/src/idot.rs:98-110,
+// matmul.rs:75-106): the same arithmetic, accumulator presets and packed fold as
+// gemv_w4a8_mma_kernel.  One tile per warp rather than a pair keeps four warps on every scheduler: a
+// chunk is a chain of shared-memory loads, MMAs and a sequential fold, and with two warps per
+// scheduler the issue slots stood empty two thirds of the time.  In a gate/up launch the up warp hands
+// its values to the gate warp of the pair through shared memory for the SwiGLU.  An expert's weights
+// are fetched once per 32 rows, the activation rows once per CTA instead of once per warp.  The
+// ordered combine is not fused here (at these batch sizes it is a launch of its own).
 #pragma once
 #include "kernels_mma.cuh"
 
 namespace pgb {
 
-constexpr int kBlkW = 8;                  // consumer warps = tile pairs per work item
-constexpr int kBlkThreads = (kBlkW + 1) * 32;
+constexpr int kBlkW = 8;                  // tile pairs per work item
+constexpr int kBlkCW = 2 * kBlkW;         // consumer warps: one tile each
+constexpr int kBlkThreads = (kBlkCW + 1) * 32;
 constexpr int kBlkRows = 32;              // activation rows per pass
 constexpr int kBlkStages = 4;
 constexpr int kBlkXOff = kBlkW * kStageBytes;
 constexpr int kBlkCsOff = kBlkXOff + kBlkRows * kXqChunkRowBytes;
 constexpr int kBlkStageBytes = kBlkCsOff + kBlkRows * kChunkBlocks * 4;
 constexpr int kBlkBarOff = kBlkStages * kBlkStageBytes;
-constexpr int kBlkCumOff = kBlkBarOff + 128;
+constexpr int kBlkCumOff = kBlkBarOff + 256;   // barriers: full[4], empty[4], then ready[8] and free[8] of the pairs
 constexpr int kBlkMaxSlots = 320;         // slots of a launch (experts of a layer + the shared one)
-constexpr int kBlkSmemBytes = kBlkCumOff + 2 * (kBlkMaxSlots + 1) * 4 + 64;
+constexpr int kBlkXchOff = kBlkCumOff + 2 * (kBlkMaxSlots + 1) * 4 + 64;   // up -> gate hand-over: [pair][nt][j][lane]
+constexpr int kBlkMaxUnits = 1024;        // (slot, row block) units of a launch
+constexpr int kBlkQueue = 8;              // item numbers in flight between producer and consumers
+constexpr int kBlkQueueOff = kBlkXchOff + kBlkW * 4 * 4 * 32 * 4;
+constexpr int kBlkUnitOff = kBlkQueueOff + kBlkQueue * 4 + 32;
+constexpr int kBlkSmemBytes = kBlkUnitOff + kBlkMaxUnits * 4;
+
+// Work items of a launch are handed out through one counter in device memory (first word: next item,
+// second word: CTAs that have finished; the last one to finish clears both), so launches that use it
+// must not overlap on a device.  Zero when the module is loaded.
+__device__ unsigned g_blk_dyn[2];
 
 struct BlkItem {
-    int slot, tb, row0, nrows, npass;
+    int slot, tb, row0, nrows;  // rows [row0, row0 + nrows) of the slot: at most 32
     const uint8_t *a, *b;  // this warp's tile streams (nullptr: no tile for this warp)
     const float *a_rs, *b_rs;
     int tile;              // this warp's tile pair index
 };
 
-// One chunk of one item for one consumer warp: NT column groups of 8 rows.
+// One chunk of one item for one consumer warp (one 16-row tile): NT column groups of 8 rows.
+// `wst` points at the tile's chunk in the stage.
 template <int NT, bool GROUPED, int BPG>
 __device__ __forceinline__ void blk_chunk(const uint8_t *wst, const uint8_t *xst, const uint8_t *cst, int g, int t,
-                                          float (&acc)[2][4][4], int (&iacc)[2][4][4], float neg_zero) {
+                                          float (&acc)[4][4], int (&iacc)[4][4], float neg_zero) {
     constexpr int GPC = kChunkBlocks / BPG;
 #pragma unroll
     for (int gi = 0; gi < GPC; ++gi) {
-        int c[2][NT][4];
+        int c[NT][4];
         int cinit[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -59,48 +76,36 @@ __device__ __forceinline__ void blk_chunk(const uint8_t *wst, const uint8_t *xst
 #pragma unroll
         for (int b = 0; b < BPG; ++b) {
             const int blk = gi * BPG + b;
-            uint32_t b0[NT], b1[NT];
+            const uint8_t *wp = wst + blk * kSlabBytes + t * 4;
+            const uint32_t w0 = *reinterpret_cast<const uint32_t *>(wp + g * 16);
+            const uint32_t w1 = *reinterpret_cast<const uint32_t *>(wp + (g + 8) * 16);
+            const uint32_t a0 = w0 & 0x0F0F0F0Fu, a2 = (w0 >> 4) & 0x0F0F0F0Fu;
+            const uint32_t a1 = w1 & 0x0F0F0F0Fu, a3 = (w1 >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 // columns past the pass's rows read stale shared memory: their results are never stored
                 const uint8_t *xr = xst + (8 * nt + g) * kXqChunkRowBytes + blk * 32 + 4 * t;
-                b0[nt] = *reinterpret_cast<const uint32_t *>(xr);
-                b1[nt] = *reinterpret_cast<const uint32_t *>(xr + 16);
-            }
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint8_t *wp = wst + h * kChunkMaxBytes + blk * kSlabBytes + t * 4;
-                const uint32_t w0 = *reinterpret_cast<const uint32_t *>(wp + g * 16);
-                const uint32_t w1 = *reinterpret_cast<const uint32_t *>(wp + (g + 8) * 16);
-                const uint32_t a0 = w0 & 0x0F0F0F0Fu, a2 = (w0 >> 4) & 0x0F0F0F0Fu;
-                const uint32_t a1 = w1 & 0x0F0F0F0Fu, a3 = (w1 >> 4) & 0x0F0F0F0Fu;
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    if (b == 0)
-                        mma_u8s8_c(c[h][nt], a0, a1, a2, a3, b0[nt], b1[nt], cinit[nt][0], cinit[nt][1]);
-                    else
-                        mma_u8s8(c[h][nt], a0, a1, a2, a3, b0[nt], b1[nt]);
-                }
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xr);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t *>(xr + 16);
+                if (b == 0)
+                    mma_u8s8_c(c[nt], a0, a1, a2, a3, b0, b1, cinit[nt][0], cinit[nt][1]);
+                else
+                    mma_u8s8(c[nt], a0, a1, a2, a3, b0, b1);
             }
         }
         if (GROUPED) {
+            const float *sp = reinterpret_cast<const float *>(wst + kChunkSlabBytes);
+            const float sc_lo = sp[g * GPC + gi], sc_hi = sp[(g + 8) * GPC + gi];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const float *sp = reinterpret_cast<const float *>(wst + h * kChunkMaxBytes + kChunkSlabBytes);
-                const float sc_lo = sp[g * GPC + gi], sc_hi = sp[(g + 8) * GPC + gi];
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    fold_pair(acc[h][nt][0], acc[h][nt][1], c[h][nt][0], c[h][nt][1], sc_lo, kMagicF, neg_zero);
-                    fold_pair(acc[h][nt][2], acc[h][nt][3], c[h][nt][2], c[h][nt][3], sc_hi, kMagicF, neg_zero);
-                }
+            for (int nt = 0; nt < NT; ++nt) {
+                fold_pair(acc[nt][0], acc[nt][1], c[nt][0], c[nt][1], sc_lo, kMagicF, neg_zero);
+                fold_pair(acc[nt][2], acc[nt][3], c[nt][2], c[nt][3], sc_hi, kMagicF, neg_zero);
             }
         } else {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) iacc[h][nt][i] += c[h][nt][i];
+                for (int i = 0; i < 4; ++i) iacc[nt][i] += c[nt][i];
         }
     }
 }
@@ -120,54 +125,99 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
 
     const int n_slots = min(*P.n_slots, kBlkMaxSlots);
     const int n_tb = (P.warp_tiles + kBlkW - 1) / kBlkW;
-    // Slots in order of falling row count (ties by index): an item of an expert with 32 rows costs four
-    // times the tensor-core and fold work of one with 8, so the items are dealt heaviest first and in
-    // serpentine order over the CTAs (round 0: CTA b takes item b, round 1: item 2G - 1 - b, ...), which
-    // evens out the sums without a shared counter.
+    // Work is cut into units (slot, block of `rpp` rows) times tile blocks.  rpp is 32 unless that
+    // leaves fewer than two items per CTA (few experts in the launch: an expert-parallel rank, a single
+    // matrix product), then 16, then 8: a unit of 8 rows streams the expert's weights again (from L2)
+    // but four CTAs share the tensor-core and fold work of a 32-row expert.  Units are numbered
+    // heaviest first (full units, then the ragged ends by falling row count) and handed out through a
+    // counter: a CTA takes the next number when it has room in its ring, whatever the others hold.
+    // (Dealing fixed shares left the CTAs with the heavy items a third longer at work than the rest.)
     int *nrow_s = cum;                      // [n_slots] row counts
-    int *order = cum + kBlkMaxSlots + 1;    // [n_active] slot of rank r
+    int *units = reinterpret_cast<int *>(smem + kBlkUnitOff);   // [n_units] slot | first row << 16
+    __shared__ int s_rpp, s_nfull, s_units;
     for (int s = tid; s < n_slots; s += blockDim.x) nrow_s[s] = P.slots[s].nrows;
     if (tid == 0) {
         for (int s = 0; s < kBlkStages; ++s) {
             mbar_init(full_b + s * 8, 1);
-            mbar_init(empty_b + s * 8, kBlkW);
+            mbar_init(empty_b + s * 8, kBlkCW);
         }
+        for (int p = 0; p < 2 * kBlkW; ++p) mbar_init(full_b + 64 + p * 8, 1);
         fence_mbar_init();
         fence_proxy_async();
     }
     __syncthreads();
-    for (int s = tid; s < n_slots; s += blockDim.x) {
-        const int nr = nrow_s[s];
-        if (nr > 0) {
-            int rank = 0;
-            for (int o = 0; o < n_slots; ++o) {
-                const int no = nrow_s[o];
-                rank += (no > nr || (no == nr && o < s)) ? 1 : 0;
+    if (warp == 0) {
+        int u32 = 0, u16 = 0, u8 = 0;
+        for (int s = lane; s < n_slots; s += 32) {
+            const int nr = nrow_s[s];
+            u32 += (nr + 31) >> 5;
+            u16 += (nr + 15) >> 4;
+            u8 += (nr + 7) >> 3;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            u32 += __shfl_xor_sync(0xffffffffu, u32, o);
+            u16 += __shfl_xor_sync(0xffffffffu, u16, o);
+            u8 += __shfl_xor_sync(0xffffffffu, u8, o);
+        }
+        const int want = 2 * (int)gridDim.x;
+        int rpp = 32;
+        if (u32 * n_tb < want) rpp = (u16 * n_tb < want) ? 8 : 16;
+        if (((rpp == 8) ? u8 : (rpp == 16 ? u16 : u32)) > kBlkMaxUnits) rpp = 32;  // (never at these batch sizes)
+        // full units first, in slot order: an exclusive scan of nrows / rpp over the slots
+        int base = 0;
+        for (int s0 = 0; s0 < n_slots; s0 += 32) {
+            const int s = s0 + lane;
+            const int nf = s < n_slots ? nrow_s[s] / rpp : 0;
+            int inc = nf;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += v;
             }
-            order[rank] = s;
+            const int first = base + inc - nf;
+            for (int p = 0; p < nf; ++p)
+                if (first + p < kBlkMaxUnits) units[first + p] = s | ((p * rpp) << 16);
+            base += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) {
+            s_rpp = rpp;
+            s_nfull = min(base, kBlkMaxUnits);
         }
     }
-    __shared__ int s_active;
-    if (tid == 0) {
-        int n = 0;
-        for (int s = 0; s < n_slots; ++s) n += nrow_s[s] > 0 ? 1 : 0;
-        s_active = n;
+    __syncthreads();
+    {
+        const int rpp = s_rpp, nfull = s_nfull;
+        for (int s = tid; s < n_slots; s += blockDim.x) {
+            const int nr = nrow_s[s], rem = nr % rpp;
+            if (rem > 0) {
+                int rank = 0;
+                for (int o = 0; o < n_slots; ++o) {
+                    const int ro = nrow_s[o] % rpp;
+                    rank += (ro > rem || (ro == rem && o < s)) ? 1 : 0;
+                }
+                if (nfull + rank < kBlkMaxUnits) units[nfull + rank] = s | ((nr - rem) << 16);
+            }
+        }
+        if (warp == 0) {
+            int n = 0;
+            for (int s = lane; s < n_slots; s += 32) n += (nrow_s[s] % rpp) > 0 ? 1 : 0;
+            for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+            if (lane == 0) s_units = min(nfull + n, kBlkMaxUnits);
+        }
     }
     __syncthreads();
-    const int total = s_active * n_tb;
+    const int rpp = s_rpp;
+    const int total = s_units * n_tb;
 
-    // the k-th item of this CTA -> index in the dealing order -> (slot, tile block)
-    const int G = gridDim.x;
-    auto item_index = [&](int k) { return k * G + ((k & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x); };
+    volatile int *queue = reinterpret_cast<volatile int *>(smem + kBlkQueueOff);
     auto decode = [&](int i, BlkItem &it, int w) {
-        const int r = i / n_tb;
-        const int slot = order[r];
+        const int u = i / n_tb;
+        const int unit = units[u];
+        const int slot = unit & 0xffff, r0 = unit >> 16;
         const GemvSlot *s = P.slots + slot;
         it.slot = slot;
-        it.tb = i - r * n_tb;
-        it.nrows = s->nrows;
-        it.npass = (s->nrows + kBlkRows - 1) / kBlkRows;
-        it.row0 = s->row0;
+        it.tb = i - u * n_tb;
+        it.nrows = min(rpp, s->nrows - r0);
+        it.row0 = s->row0 + r0;
         it.tile = it.tb * kBlkW + w;
         it.a = it.b = nullptr;
         it.a_rs = s->a_rs;
@@ -183,26 +233,40 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
         }
     };
 
-    if (warp == kBlkW) {
+    if (warp == kBlkCW) {
         // ======================================================= producer warp
-        // lane w < 8: the chunk (pair) of consumer warp w; lane 8: the pass's activation rows of the
+        // lane w < 8: the chunks of tile pair w; lane 8: the pass's activation rows of the
         // chunk; lane 9: their block sums
         uint32_t q = 0;
         bool ok = true;
-        for (int k = 0; ok; ++k) {
-            const int i = item_index(k);
+        for (int n = 0; ok; ++n) {
+            int i = 0;
+            if (lane == 0) i = (int)atomicAdd(&g_blk_dyn[0], 1u);
+            i = __shfl_sync(0xffffffffu, i, 0);
             if (i >= total) {
-                if (k * G >= total) break;
-                continue;  // this round has fewer items than CTAs
+                // end marker: an empty stage whose queue entry is -1
+                const uint32_t stage = q % kBlkStages;
+                if (q >= kBlkStages) {
+                    const bool fine = mbar_wait_bounded(empty_b + stage * 8, ((q / kBlkStages) + 1) & 1u);
+                    if (__any_sync(0xffffffffu, !fine)) {
+                        if (lane == 0) report_error(P.err, kErrBarrierTimeout);
+                        break;
+                    }
+                }
+                if (lane == 0) {
+                    queue[n % kBlkQueue] = -1;
+                    mbar_arrive(full_b + stage * 8);
+                }
+                break;
             }
             BlkItem it;
             decode(i, it, lane < kBlkW ? lane : 0);
             const int my_bytes = (lane < kBlkW && it.a) ? (it.b ? 2 : 1) * CHUNK_BYTES : 0;
             int wbytes = my_bytes;
             for (int o = 16; o > 0; o >>= 1) wbytes += __shfl_xor_sync(0xffffffffu, wbytes, o);
-            for (int pc = 0; pc < it.npass * P.nchunk; ++pc, ++q) {
-                const int pass = pc / P.nchunk, chunk = pc - pass * P.nchunk;
-                const int first = it.row0 + pass * kBlkRows, nr = min(kBlkRows, it.nrows - pass * kBlkRows);
+            for (int pc = 0; pc < P.nchunk; ++pc, ++q) {
+                const int chunk = pc;
+                const int first = it.row0, nr = it.nrows;
                 const uint32_t stage = q % kBlkStages;
                 if (q >= kBlkStages) {
                     const bool fine = mbar_wait_bounded(empty_b + stage * 8, ((q / kBlkStages) + 1) & 1u);
@@ -215,6 +279,7 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
                 const uint32_t bar = full_b + stage * 8;
                 const uint32_t dst = smem_u + stage * kBlkStageBytes;
                 if (lane == 0) {
+                    if (pc == 0) queue[n % kBlkQueue] = i;  // read by the consumers once this stage is full
                     fence_proxy_async();
                     mbar_expect_tx(bar, wbytes + nr * (kXqChunkRowBytes + kChunkBlocks * 4));
                 }
@@ -231,44 +296,56 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
                 }
             }
         }
-        return;
-    }
+    } else {
     // =========================================================== consumer warps
-    uint32_t q = 0;
-    float acc[2][4][4];
-    int iacc[2][4][4];
+    const int pair = warp >> 1, half = warp & 1;
+    float *xch = reinterpret_cast<float *>(smem + kBlkXchOff) + pair * (4 * 4 * 32);
+    const uint32_t ready_b = full_b + 64 + pair * 8, free_b = full_b + 64 + (kBlkW + pair) * 8;
+    uint32_t q = 0, n_epi = 0;  // n_epi: hand-overs of this pair so far
+    float acc[4][4];
+    int iacc[4][4];
     bool ok = true;
-    for (int k = 0; ok; ++k) {
-        const int i = item_index(k);
-        if (i >= total) {
-            if (k * G >= total) break;
-            continue;
+    for (int n = 0; ok; ++n) {
+        // the first stage of the next item (or the end marker) tells which item it is
+        {
+            const bool fine = mbar_wait_bounded(full_b + (q % kBlkStages) * 8, (q / kBlkStages) & 1u);
+            if (__any_sync(0xffffffffu, !fine)) {
+                if (lane == 0) report_error(P.err, kErrBarrierTimeout);
+                break;
+            }
         }
+        const int i = queue[n % kBlkQueue];
+        if (i < 0) break;
+        bool first_stage = true;
         BlkItem it;
-        decode(i, it, warp);
-        for (int pass = 0; pass < it.npass && ok; ++pass) {
-            const int row0 = it.row0 + pass * kBlkRows, nr = min(kBlkRows, it.nrows - pass * kBlkRows);
+        decode(i, it, pair);
+        // this warp's tile: gate / up tile of the pair (mode 0), down tiles 2t / 2t + 1 (mode 1)
+        const bool have = half ? (it.a != nullptr && it.b != nullptr) : (it.a != nullptr);
+        do {  // (one pass; `continue` leaves it)
+            const int row0 = it.row0, nr = it.nrows;
             const int nt_n = (nr + 7) >> 3;
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        acc[h][nt][j] = 0.0f;
-                        iacc[h][nt][j] = 0;
-                    }
-            for (int chunk = 0; chunk < P.nchunk; ++chunk, ++q) {
-                const uint32_t stage = q % kBlkStages;
-                const bool fine = mbar_wait_bounded(full_b + stage * 8, (q / kBlkStages) & 1u);
-                if (__any_sync(0xffffffffu, !fine)) {
-                    if (lane == 0) report_error(P.err, kErrBarrierTimeout);
-                    ok = false;
-                    break;
+                for (int j = 0; j < 4; ++j) {
+                    acc[nt][j] = 0.0f;
+                    iacc[nt][j] = 0;
                 }
-                if (it.a) {
+            for (int chunk = 0; chunk < P.nchunk && ok; ++chunk, ++q) {
+                const uint32_t stage = q % kBlkStages;
+                if (!first_stage) {
+                    const bool fine = mbar_wait_bounded(full_b + stage * 8, (q / kBlkStages) & 1u);
+                    if (__any_sync(0xffffffffu, !fine)) {
+                        if (lane == 0) report_error(P.err, kErrBarrierTimeout);
+                        ok = false;
+                        break;
+                    }
+                }
+                first_stage = false;
+                if (have) {
                     const uint8_t *st = smem + stage * kBlkStageBytes;
-                    const uint8_t *wst = st + warp * kStageBytes, *xst = st + kBlkXOff, *cst = st + kBlkCsOff;
+                    const uint8_t *wst = st + pair * kStageBytes + half * kChunkMaxBytes;
+                    const uint8_t *xst = st + kBlkXOff, *cst = st + kBlkCsOff;
                     switch (nt_n) {
                         case 1: blk_chunk<1, GROUPED, BPG>(wst, xst, cst, g, t, acc, iacc, P.neg_zero); break;
                         case 2: blk_chunk<2, GROUPED, BPG>(wst, xst, cst, g, t, acc, iacc, P.neg_zero); break;
@@ -279,60 +356,107 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_b + stage * 8);
             }
-            if (!ok || !it.a) continue;
+            if (!ok) continue;
             // ---- epilogue of the pass: activation scale, SwiGLU (mode 0), stores, row maxima
-            auto value = [&](int h, int nt, int j, int o) -> float {
+            auto value = [&](int nt, int j, int o) -> float {
                 const int rr = min(8 * nt + 2 * t + (j & 1), nr - 1);
                 const float sxa = P.sx[row0 + rr];
-                if (GROUPED) return __fmul_rn(acc[h][nt][j], sxa);
-                const float *rsp = (P.mode == 0 && h) ? it.b_rs : it.a_rs;
+                if (GROUPED) return __fmul_rn(acc[nt][j], sxa);
+                const float *rsp = (P.mode == 0 && half) ? it.b_rs : it.a_rs;
                 const float rs = (o < P.ntile * 16) ? rsp[o] : 0.0f;
-                return __fmul_rn(__fmul_rn((float)iacc[h][nt][j], rs), sxa);  // block corrections rode in the MMA start values
+                return __fmul_rn(__fmul_rn((float)iacc[nt][j], rs), sxa);  // block corrections rode in the MMA start values
             };
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                if (nt >= nt_n) break;
-                float amax2[2] = {0.0f, 0.0f};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int ridx = 8 * nt + 2 * t + (j & 1);
-                    const bool valid = ridx < nr;
-                    const int r = g + 8 * (j >> 1);
-                    if (P.mode == 0) {
-                        const int o = it.tile * 16 + r;
-                        const float vg = value(0, nt, j, o), vu = value(1, nt, j, o);
-                        if (valid && o < P.O) {
-                            const float hval = __fmul_rn(silu32(vg), vu);
-                            P.out[(long long)(row0 + ridx) * P.out_stride + o] = hval;
-                            const float a = fabsf(hval);
-                            if (a == a) amax2[j & 1] = fmaxf(amax2[j & 1], a);  // NaN never becomes the maximum
+            if (P.mode == 0) {
+                // the up warp hands its values to the gate warp of the pair (bounded waits on both sides:
+                // a warp that gave up leaves its partner to run out of patience, not to hang)
+                if (half == 1) {
+                    if (n_epi > 0) {
+                        const bool fine = mbar_wait_bounded(free_b, (n_epi + 1) & 1u);
+                        if (__any_sync(0xffffffffu, !fine)) {
+                            if (lane == 0) report_error(P.err, kErrBarrierTimeout);
+                            ok = false;
+                            continue;
                         }
-                    } else {
+                    }
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int o = (2 * it.tile + h) * 16 + r;
-                            const float v = value(h, nt, j, o);
-                            if (valid && o < P.O && (h == 0 || it.b))
-                                P.out[(long long)(row0 + ridx) * P.out_stride + o] = v;
+                    for (int nt = 0; nt < 4; ++nt) {
+                        if (nt >= nt_n) break;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            xch[(nt * 4 + j) * 32 + lane] = have ? value(nt, j, it.tile * 16 + g + 8 * (j >> 1)) : 0.0f;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(ready_b);
+                } else {
+                    const bool fine = mbar_wait_bounded(ready_b, n_epi & 1u);
+                    if (__any_sync(0xffffffffu, !fine)) {
+                        if (lane == 0) report_error(P.err, kErrBarrierTimeout);
+                        ok = false;
+                        continue;
+                    }
+                }
+                ++n_epi;
+                if (half == 0 && have) {
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        if (nt >= nt_n) break;
+                        float amax2[2] = {0.0f, 0.0f};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int ridx = 8 * nt + 2 * t + (j & 1);
+                            const int o = it.tile * 16 + g + 8 * (j >> 1);
+                            const float vg = value(nt, j, o), vu = xch[(nt * 4 + j) * 32 + lane];
+                            if (ridx < nr && o < P.O) {
+                                const float hval = __fmul_rn(silu32(vg), vu);
+                                P.out[(long long)(row0 + ridx) * P.out_stride + o] = hval;
+                                const float a = fabsf(hval);
+                                if (a == a) amax2[j & 1] = fmaxf(amax2[j & 1], a);  // NaN never becomes the maximum
+                            }
+                        }
+                        if (P.amax_out != nullptr) {
+                            // row maxima of |h|: reduce over the 8 lanes that share this lane's two columns
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                float a = amax2[j];
+                                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+                                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 8));
+                                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+                                const int ridx = 8 * nt + 2 * t + j;
+                                if (g == 0 && ridx < nr && a > 0.0f)
+                                    atomicMax(P.amax_out + row0 + ridx, __float_as_uint(a));
+                            }
                         }
                     }
                 }
-                if (P.mode == 0 && P.amax_out != nullptr) {
-                    // row maxima of |h|: reduce over the 8 lanes that share this lane's two columns
+                if (half == 0) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(free_b);  // the hand-over area is free again
+                }
+            } else if (have) {
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        float a = amax2[j];
-                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
-                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 8));
-                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
-                        const int ridx = 8 * nt + 2 * t + j;
-                        if (g == 0 && ridx < nr && a > 0.0f) atomicMax(P.amax_out + row0 + ridx, __float_as_uint(a));
+                for (int nt = 0; nt < 4; ++nt) {
+                    if (nt >= nt_n) break;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int ridx = 8 * nt + 2 * t + (j & 1);
+                        const int o = (2 * it.tile + half) * 16 + g + 8 * (j >> 1);
+                        const float v = value(nt, j, o);
+                        if (ridx < nr && o < P.O) P.out[(long long)(row0 + ridx) * P.out_stride + o] = v;
                     }
                 }
             }
+        } while (false);
+    }
+    }
+    // every CTA passes here, also after a failed wait: the last one re-arms the counter
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&g_blk_dyn[1], 1u) == gridDim.x - 1) {
+            g_blk_dyn[0] = 0u;
+            g_blk_dyn[1] = 0u;
+            __threadfence();
         }
-        // the same warp ran every pass of this (expert, tile pair): its arrival completes the expert's share
-        if (ok && it.a && P.mode == 1 && P.comb.col_done != nullptr) ordered_combine_tile(P, it.tile, lane, n_slots);
     }
 }
 

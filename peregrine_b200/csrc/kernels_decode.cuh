@@ -55,8 +55,9 @@ struct DecodeArgs {
     unsigned *sync;      // zero at launch: [0] CTAs whose logits are written, [1] CTAs that left,
                          // [2 + a] warps done with gate/up of attempt a, [8 + a * n_col + t] column tiles
     int n_col;
-    unsigned *exact_flag;  // set to `epoch` by the chain CTA that wrote the exact plan
-    unsigned epoch;
+    unsigned *exact_flag;  // set to the step number by the chain CTA that wrote the exact plan
+    unsigned *epoch_word;  // the step number, in device memory: read at the start of a launch, advanced by the last
+                           // worker CTA to leave, so the same arguments serve every launch (graph replays too)
     float *out;            // [D]
     unsigned long long *timeline;  // optional [gridDim.x][16] globaltimer stamps (ns) per CTA, see decode_stamp
 };
@@ -244,6 +245,8 @@ template <bool GROUPED, int BPG>
 __global__ void __launch_bounds__(kGemvThreads, 1) decode_step_kernel(const DecodeArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    unsigned epoch = 0;  // lane 0 of every warp holds it (only lane 0 ever compares or publishes it)
+    if (lane == 0) epoch = __ldcg(A.epoch_word);
     if ((int)blockIdx.x < A.n_chain) {
         if (tid == 0) decode_stamp(A, 0);
         const bool planned = route_chain_role(A.route, smem, blockIdx.x);
@@ -251,7 +254,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_step_kernel(const Deco
         if (planned) {  // uniform over the CTA
             __threadfence();
             __syncthreads();
-            if (tid == 0) st_release_u32(A.exact_flag, A.epoch);
+            if (tid == 0) st_release_u32(A.exact_flag, epoch);
         }
         return;
     }
@@ -521,7 +524,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_step_kernel(const Deco
                 // normally is, long since), so the end of the step does not wait for these round trips
                 if (first < A.n_col && !exact_seen) {
                     int there = 0;
-                    if (lane == 0) there = ld_acquire_u32(A.exact_flag) == A.epoch;
+                    if (lane == 0) there = ld_acquire_u32(A.exact_flag) == epoch;
                     if (__shfl_sync(0xffffffffu, there, 0)) fetch_exact();
                 }
             }
@@ -551,7 +554,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_step_kernel(const Deco
             bool go = true;
             if (lane == 0) decode_stamp(A, 9);
             if (!exact_seen) {
-                if (!warp_wait_counter(A.exact_flag, A.epoch, true, lane)) {
+                if (!warp_wait_counter(A.exact_flag, epoch, true, lane)) {
                     if (lane == 0) report_error(A.route.err, kErrBarrierTimeout);
                     go = false;
                 } else {
@@ -595,7 +598,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_step_kernel(const Deco
         if (warp == 0) {
             int mismatch = 0;
             if (attempt == 0) {
-                if (!warp_wait_counter(A.exact_flag, A.epoch, true, lane)) {
+                if (!warp_wait_counter(A.exact_flag, epoch, true, lane)) {
                     if (lane == 0) report_error(A.route.err, kErrBarrierTimeout);
                 } else {
                     const int e_idx = lane < k ? __ldcg(A.route.plan.idx + lane) : 0;
@@ -616,8 +619,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_step_kernel(const Deco
         ctl[37] = (atomicAdd(A.sync + 1, 1u) == (unsigned)(W - 1)) ? 1 : 0;
     }
     __syncthreads();
-    if (ctl[37])
+    if (ctl[37]) {
         for (int i = tid; i < 8 + 2 * A.n_col; i += blockDim.x) A.sync[i] = 0u;
+        // every CTA of this launch has read the step number (the workers have all arrived here, the
+        // chain CTAs finished before the plan the workers waited for); zero is never a step number
+        if (tid == 0) *A.epoch_word = (epoch + 1u != 0u) ? epoch + 1u : 1u;
+    }
 }
 
 }  // namespace pgb

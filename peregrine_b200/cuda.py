@@ -43,7 +43,7 @@ SYMBOLS = [
     "coli_cuda_tensor_upload_grouped", "coli_cuda_moe_layer_create", "coli_cuda_moe_layer_set_expert",
     "coli_cuda_moe_layer_free", "coli_cuda_moe_layer_forward_dev", "coli_cuda_moe_layer_forward",
     "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_set_spec",
-    "coli_cuda_moe_layer_set_fused", "coli_cuda_int8_peak_probe", "coli_cuda_tensor_clone", "coli_cuda_moe_layer_set_bias", "coli_cuda_moe_layer_decode_timeline", "coli_cuda_moe_layer_last_pairs",
+    "coli_cuda_moe_layer_set_fused", "coli_cuda_int8_peak_probe", "coli_cuda_tensor_clone", "coli_cuda_moe_layer_set_bias", "coli_cuda_moe_layer_decode_timeline", "coli_cuda_moe_layer_host_times", "coli_cuda_moe_layer_last_pairs",
     "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_ep_create",
     "coli_cuda_ep_block_bytes", "coli_cuda_ep_local_base", "coli_cuda_ep_export", "coli_cuda_ep_attach",
     "coli_cuda_ep_attach_ptr", "coli_cuda_ep_free", "coli_cuda_ep_reset", "coli_cuda_moe_layer_ep_route_dev",
@@ -133,6 +133,7 @@ def lib():
         L.coli_cuda_int8_peak_probe.restype = C.c_double
         L.coli_cuda_moe_layer_set_bias.argtypes = [vp, vp]
         L.coli_cuda_moe_layer_decode_timeline.argtypes = [vp, i, vp, i, vp, vp]
+        L.coli_cuda_moe_layer_host_times.argtypes = [vp, vp, vp, i]
         L.coli_cuda_moe_layer_last_pairs.argtypes = [vp, vp, vp, vp, i]
         L.coli_cuda_moe_layer_read_taps.argtypes = [vp, vp, sz, vp, sz]
         L.coli_cuda_moe_layer_set_ep.argtypes = [vp, i, i]
@@ -500,12 +501,27 @@ class MoeLayer:
     def set_shared(self, expert: GpuExpert):
         self.set_expert(self.n_experts, expert)
 
-    def forward(self, x) -> np.ndarray:
-        x = _f32(x).reshape(-1, self.hidden)
-        out = np.empty_like(x)
-        if lib().coli_cuda_moe_layer_forward(self.handle, _ptr(out), _ptr(x), x.shape[0]) != 1:
+    def forward(self, x, out: np.ndarray | None = None) -> np.ndarray:
+        """Blocking layer step on host rows.  With ``out`` (C-contiguous fp32 of x's shape) and a
+        C-contiguous fp32 ``x`` no array is allocated or converted on the way in."""
+        if out is None or x.dtype != np.float32 or not x.flags.c_contiguous:
+            x = _f32(x).reshape(-1, self.hidden)
+            if out is None:
+                out = np.empty_like(x)
+        if out.dtype != np.float32 or not out.flags.c_contiguous or out.size != x.size:
+            raise ValueError("moe layer forward: out must be C-contiguous fp32 of x's size")
+        if lib().coli_cuda_moe_layer_forward(self.handle, out.ctypes.data, x.ctypes.data,
+                                             x.size // self.hidden) != 1:
             raise CudaError("cuda moe_layer_forward failed")
         return out
+
+    def host_times(self, reset: bool = True):
+        """Mean host-side microseconds per blocking ``forward`` since the last reset, by part."""
+        us = (C.c_double * 5)()
+        n = C.c_uint64(0)
+        lib().coli_cuda_moe_layer_host_times(self.handle, us, C.byref(n), int(reset))
+        names = ("stage_x", "enqueue_upload", "enqueue_launches", "wait_device", "copy_out")
+        return {k: us[j] / max(n.value, 1) for j, k in enumerate(names)}, int(n.value)
 
     def forward_dev(self, out_ptr: int, x_ptr: int, m: int):
         if lib().coli_cuda_moe_layer_forward_dev(self.handle, C.c_void_p(out_ptr), C.c_void_p(x_ptr), m) != 1:

@@ -193,6 +193,42 @@ def test_speculative_routing_modes_agree_bit_for_bit(dev, m):
     ml.free()
 
 
+def test_blocking_single_token_calls_replay_a_graph(dev):
+    """The blocking one-token call records its upload and the single-launch step as a graph after the
+    first plain run.  Replays (recognisable by no separate upload being enqueued) give the oracle's
+    rows for every new token; a setter that changes the layer drops the graph."""
+    import os
+
+    if os.environ.get("PEREGRINE_B200_FORWARD_GRAPH") == "0" or os.environ.get("PEREGRINE_B200_FUSED_DECODE") == "0":
+        pytest.skip("graph replay of the blocking call is switched off")
+    layer = synth_layer(77, hidden=512, inter=160, n_experts=40, k=4, gs=32)
+    xs = synth_tokens(78, 7, 512)
+    wants = [oracle_layer_forward(layer, xs[i:i + 1], threads=4, want_routing=True) for i in range(7)]
+    ml = upload_layer(dev, layer)
+    out = np.empty((1, 512), np.float32)
+    assert np.array_equal(bits(ml.forward(xs[0:1], out)), bits(wants[0][0]))  # plain; records the graph
+    ml.host_times(reset=True)
+    for i in range(1, 5):
+        got = ml.forward(xs[i:i + 1], out)
+        assert np.array_equal(bits(got), bits(wants[i][0])), f"replay {i}"
+        gidx, gw, gkeff, guni = ml.last_routing(1)
+        assert np.array_equal(gidx, wants[i][1]) and np.array_equal(bits(gw), bits(wants[i][2]))
+    us, n = ml.host_times(reset=True)
+    assert n == 4 and us["enqueue_upload"] == 0.0
+    ml.set_spec(2)  # the speculative pick forced wrong: same graph shape, but the layer changed
+    assert np.array_equal(bits(ml.forward(xs[5:6], out)), bits(wants[5][0]))
+    us, n = ml.host_times(reset=True)
+    assert n == 1 and us["enqueue_upload"] > 0.0  # a plain call again (and a new recording)
+    assert np.array_equal(bits(ml.forward(xs[6:7], out)), bits(wants[6][0]))  # replay under mode 2
+    ml.set_spec(0)  # exact routing first: separate launches, nothing to record
+    for i in (1, 2):
+        assert np.array_equal(bits(ml.forward(xs[i:i + 1], out)), bits(wants[i][0]))
+    us, n = ml.host_times(reset=True)
+    assert us["enqueue_upload"] > 0.0
+    assert cuda.last_device_error(dev) == 0
+    ml.free()
+
+
 @pytest.mark.parametrize("kernel", ["1", "2"])  # 1: mma.sync tiles, 2: tcgen05 tiles
 @pytest.mark.parametrize("gs,hidden,inter,m", [(0, 256, 96, 140), (32, 512, 160, 200), (128, 384, 256, 150),
                                                (64, 512, 128, 37)])
