@@ -559,7 +559,13 @@ static int block_launch_t(Ctx *c, const GemvParams &P) {
     if (!ensure_smem(c, kfn, (size_t)kBlkSmemBytes, "block gemv shared-memory opt-in")) return 0;
     return launch(kfn, dim3(c->sms), dim3(kBlkThreads), (size_t)kBlkSmemBytes, c->stream, "w4a8 block gemv launch", P);
 }
-static int block_launch(Ctx *c, const GemvParams &P, bool grouped, int bpg) {
+static int block_launch(Ctx *c, const GemvParams &P0, bool grouped, int bpg) {
+    static const int rpp_env = [] {
+        const char *e = std::getenv("PEREGRINE_B200_BLOCK_RPP");
+        return e ? std::atoi(e) : 0;
+    }();
+    GemvParams P = P0;
+    P.blk_rpp = rpp_env;  // 0: 32 rows per work unit
     if (!grouped) return block_launch_t<false, 1>(c, P);
     switch (bpg) {
         case 1: return block_launch_t<true, 1>(c, P);

@@ -279,6 +279,7 @@ struct GemvParams {
     int grid;  // host only: CTAs to launch (0 = one per SM)
     int pdl;   // host only: launch with programmatic stream serialisation (see griddep_wait)
     int tile_rb;  // host only: > 0 selects the large-batch tile kernel with this many row blocks in the grid
+    int blk_rpp;  // shared-row kernel: rows per work unit (16 or 8; anything else: 32)
     int umma;     // host only: with tile_rb > 0, take the tcgen05 kernel (activations in core-matrix order)
     const int *n_xrows_dev;     // rows actually valid (device scalar; nullptr: n_xrows)
     unsigned *amax_out;   // mode 0: per pair row, atomicMax of |h| bits (nullptr: off)
@@ -1633,6 +1634,7 @@ __device__ __forceinline__ void route_quantise_row(const RouteArgs &A, int row, 
 // Chain role of the routing launches, executed by CTA `cta` of A.n_chain_ctas (block size kRtThreads;
 // for a single token any larger block works too, the extra warps idle).  Returns true in the one CTA that finished
 // last and therefore wrote the plan (never when A.no_plan is set).
+// Returns true (for the whole CTA) in the chain CTA that finished last.
 __device__ __forceinline__ bool route_chain_role(const RouteArgs &A, unsigned char *rt_smem, int cta) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_eblk = (A.E + kRtEPB - 1) / kRtEPB;
@@ -1687,6 +1689,22 @@ __device__ __forceinline__ bool route_chain_role(const RouteArgs &A, unsigned ch
                              full_u32 + st * 8);
                 }
                 __syncwarp();
+                continue;
+            }
+            if (A.rwt != nullptr && A.M > 1) {
+                // the e-block's 8 padded router rows in one copy, the CTA's token rows one by one straight
+                // from x (up to 32 tokens: no re-laid copy of the tokens, one launch less per step)
+                if (lane == 0) {
+                    fence_proxy_async();
+                    mbar_expect_tx(full_u32 + st * 8, (uint32_t)(kRtEPB * kRtRowFloats * 4 + ns * dlen * 4));
+                    bulk_g2s(smem_u32(rt_smem + st * kRtStageBytes),
+                             A.rwt + ((long long)eb * nslice + i) * kRtEPB * kRtRowFloats,
+                             (uint32_t)(kRtEPB * kRtRowFloats * 4), full_u32 + st * 8);
+                }
+                __syncwarp();
+                for (int r = lane; r < ns; r += 32)
+                    bulk_g2s(smem_u32(rt_smem + st * kRtStageBytes + (xrow0 + r) * kRtRowFloats * 4),
+                             A.x + (long long)(s0 + r) * A.ldx + d0, (uint32_t)(dlen * 4), full_u32 + st * 8);
                 continue;
             }
             if (lane == 0) {
@@ -1934,8 +1952,9 @@ __device__ __forceinline__ bool route_chain_role(const RouteArgs &A, unsigned ch
         if (*s_last) *A.done_counter = 0u;
     }
     __syncthreads();
-    if (!*s_last || A.no_plan) return false;
+    if (!*s_last) return false;
     __threadfence();
+    if (A.no_plan) return true;  // the caller goes on from the complete logits
     if (A.small_plan)
         route_plan_small<true>(A.logits, A.bias, A.M, A.E, A.k, A.norm_topk, A.routed_scale, A.has_shared, A.experts,
                                A.plan, rt_smem);

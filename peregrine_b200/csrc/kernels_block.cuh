@@ -5,10 +5,10 @@
 // rows alike; beyond 8 rows per expert the rows of a 256-element chunk (272 bytes each) weigh as much
 // as the chunk's packed weights (5 KB for a tile pair), the traffic from L2 into the SM doubles and
 // an expert with more than 16 rows is streamed once per 16 rows.  Here a work item is (expert, block
-// of 8 tile pairs), run in passes of up to 32 rows: a producer warp fills a CTA-wide ring stage by stage with
-// the 8 pairs' weight chunks, ONE copy of the pass's activation rows of that chunk and their block
+// of up to 32 rows, block of 8 tile pairs): a producer warp fills a CTA-wide ring stage by stage with
+// the 8 pairs' weight chunks, ONE copy of the item's activation rows of that chunk and their block
 // sums; 16 consumer warps take one 16-row tile each (warp 2p + h: half h of pair p), multiply it with
-// all rows of the pass (m16n8k32 int8 MMAs, 1 to 4 column groups of 8 rows, chosen per item) and fold
+// all rows of the item (m16n8k32 int8 MMAs, 1 to 4 column groups of 8 rows, chosen per item) and fold
 // the group dots into fp32 in the reference's order (crates/peregrine-kernels/src/idot.rs:98-110,
 // matmul.rs:75-106): the same arithmetic, accumulator presets and packed fold as
 // gemv_w4a8_mma_kernel.  One tile per warp rather than a pair keeps four warps on every scheduler: a
@@ -24,7 +24,8 @@ namespace pgb {
 
 constexpr int kBlkW = 8;                  // tile pairs per work item
 constexpr int kBlkCW = 2 * kBlkW;         // consumer warps: one tile each
-constexpr int kBlkThreads = (kBlkCW + 1) * 32;
+constexpr int kBlkPW = 4;                 // producer warps: two tile pairs each (the first also the rows)
+constexpr int kBlkThreads = (kBlkCW + kBlkPW) * 32;
 constexpr int kBlkRows = 32;              // activation rows per pass
 constexpr int kBlkStages = 4;
 constexpr int kBlkXOff = kBlkW * kStageBytes;
@@ -37,7 +38,7 @@ constexpr int kBlkXchOff = kBlkCumOff + 2 * (kBlkMaxSlots + 1) * 4 + 64;   // up
 constexpr int kBlkMaxUnits = 1024;        // (slot, row block) units of a launch
 constexpr int kBlkQueue = 8;              // item numbers in flight between producer and consumers
 constexpr int kBlkQueueOff = kBlkXchOff + kBlkW * 4 * 4 * 32 * 4;
-constexpr int kBlkUnitOff = kBlkQueueOff + kBlkQueue * 4 + 32;
+constexpr int kBlkUnitOff = kBlkQueueOff + kBlkQueue * 4 + 32;   // (queue, then the producers' item count)
 constexpr int kBlkSmemBytes = kBlkUnitOff + kBlkMaxUnits * 4;
 
 // Work items of a launch are handed out through one counter in device memory (first word: next item,
@@ -125,13 +126,13 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
 
     const int n_slots = min(*P.n_slots, kBlkMaxSlots);
     const int n_tb = (P.warp_tiles + kBlkW - 1) / kBlkW;
-    // Work is cut into units (slot, block of `rpp` rows) times tile blocks.  rpp is 32 unless that
-    // leaves fewer than two items per CTA (few experts in the launch: an expert-parallel rank, a single
-    // matrix product), then 16, then 8: a unit of 8 rows streams the expert's weights again (from L2)
-    // but four CTAs share the tensor-core and fold work of a 32-row expert.  Units are numbered
+    // Work is cut into units (slot, block of `rpp` rows) times tile blocks; rpp = 32 unless the launch
+    // asks for 16 or 8 (P.blk_rpp).  Smaller row blocks let several CTAs share the tensor-core and fold
+    // work of an expert with many rows at the price of streaming its weights once per block; measured on
+    // launches with few experts (an expert-parallel rank) that price was the higher one (experts phase
+    // 151 us at 32 rows per unit, 162 at 16, 186 at 8), so 32 is what the host passes.  Units are numbered
     // heaviest first (full units, then the ragged ends by falling row count) and handed out through a
     // counter: a CTA takes the next number when it has room in its ring, whatever the others hold.
-    // (Dealing fixed shares left the CTAs with the heavy items a third longer at work than the rest.)
     int *nrow_s = cum;                      // [n_slots] row counts
     int *units = reinterpret_cast<int *>(smem + kBlkUnitOff);   // [n_units] slot | first row << 16
     __shared__ int s_rpp, s_nfull, s_units;
@@ -142,6 +143,7 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
             mbar_init(empty_b + s * 8, kBlkCW);
         }
         for (int p = 0; p < 2 * kBlkW; ++p) mbar_init(full_b + 64 + p * 8, 1);
+        reinterpret_cast<volatile int *>(smem + kBlkQueueOff)[kBlkQueue] = 0;  // items published so far
         fence_mbar_init();
         fence_proxy_async();
     }
@@ -159,9 +161,7 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
             u16 += __shfl_xor_sync(0xffffffffu, u16, o);
             u8 += __shfl_xor_sync(0xffffffffu, u8, o);
         }
-        const int want = 2 * (int)gridDim.x;
-        int rpp = 32;
-        if (u32 * n_tb < want) rpp = (u16 * n_tb < want) ? 8 : 16;
+        int rpp = (P.blk_rpp == 8 || P.blk_rpp == 16) ? P.blk_rpp : 32;
         if (((rpp == 8) ? u8 : (rpp == 16 ? u16 : u32)) > kBlkMaxUnits) rpp = 32;  // (never at these batch sizes)
         // full units first, in slot order: an exclusive scan of nrows / rpp over the slots
         int base = 0;
@@ -233,39 +233,73 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
         }
     };
 
-    if (warp == kBlkCW) {
-        // ======================================================= producer warp
-        // lane w < 8: the chunks of tile pair w; lane 8: the pass's activation rows of the
-        // chunk; lane 9: their block sums
+    if (warp >= kBlkCW) {
+        // ======================================================= producer warps
+        // Issuing a bulk copy costs the issuing warp ~130 cycles, one copy after the other; one warp
+        // issuing a stage's 18 copies took longer than the consumers needed for the stage.  So four
+        // warps share them: producer p issues the chunks of tile pairs 2p and 2p + 1 (lanes 0-3: pair,
+        // half), producer 0 also the item's activation rows and block sums, the byte count of the
+        // stage and the item numbers (counter -> queue; `item_seq` tells the other producers how many
+        // items have been published).
+        const int p = warp - kBlkCW;
+        volatile int *item_seq = queue + kBlkQueue;
         uint32_t q = 0;
         bool ok = true;
         for (int n = 0; ok; ++n) {
             int i = 0;
-            if (lane == 0) i = (int)atomicAdd(&g_blk_dyn[0], 1u);
-            i = __shfl_sync(0xffffffffu, i, 0);
-            if (i >= total) {
-                // end marker: an empty stage whose queue entry is -1
-                const uint32_t stage = q % kBlkStages;
-                if (q >= kBlkStages) {
-                    const bool fine = mbar_wait_bounded(empty_b + stage * 8, ((q / kBlkStages) + 1) & 1u);
-                    if (__any_sync(0xffffffffu, !fine)) {
-                        if (lane == 0) report_error(P.err, kErrBarrierTimeout);
+            if (p == 0) {
+                if (lane == 0) {
+                    i = (int)atomicAdd(&g_blk_dyn[0], 1u);
+                    if (i >= total) i = -1;
+                    queue[n % kBlkQueue] = i;  // the consumers read it once the item's first stage is full
+                    __threadfence_block();
+                    *item_seq = n + 1;
+                }
+            } else if (lane == 0) {
+                const long long t0 = clock64();
+                while (*item_seq <= n) {
+                    if (clock64() - t0 > 2000000000LL) {
+                        i = -2;
                         break;
                     }
                 }
-                if (lane == 0) {
-                    queue[n % kBlkQueue] = -1;
-                    mbar_arrive(full_b + stage * 8);
+                __threadfence_block();
+                if (i != -2) i = queue[n % kBlkQueue];
+            }
+            i = __shfl_sync(0xffffffffu, i, 0);
+            if (i == -2) {
+                if (lane == 0) report_error(P.err, kErrBarrierTimeout);
+                break;
+            }
+            if (i < 0) {
+                // end marker (producer 0): an empty stage whose queue entry is -1
+                if (p == 0) {
+                    const uint32_t stage = q % kBlkStages;
+                    if (q >= kBlkStages) {
+                        const bool fine = mbar_wait_bounded(empty_b + stage * 8, ((q / kBlkStages) + 1) & 1u);
+                        if (__any_sync(0xffffffffu, !fine)) {
+                            if (lane == 0) report_error(P.err, kErrBarrierTimeout);
+                            break;
+                        }
+                    }
+                    if (lane == 0) mbar_arrive(full_b + stage * 8);
                 }
                 break;
             }
+            // producer 0: lane w < 8 looks at pair w for the stage's byte count; every producer: lanes 0-3
+            // hold (pair 2p + lane / 2, half lane & 1)
             BlkItem it;
-            decode(i, it, lane < kBlkW ? lane : 0);
-            const int my_bytes = (lane < kBlkW && it.a) ? (it.b ? 2 : 1) * CHUNK_BYTES : 0;
-            int wbytes = my_bytes;
-            for (int o = 16; o > 0; o >>= 1) wbytes += __shfl_xor_sync(0xffffffffu, wbytes, o);
+            int wbytes = 0;
+            if (p == 0) {
+                decode(i, it, lane < kBlkW ? lane : 0);
+                wbytes = (lane < kBlkW && it.a) ? (it.b ? 2 : 1) * CHUNK_BYTES : 0;
+                for (int o = 16; o > 0; o >>= 1) wbytes += __shfl_xor_sync(0xffffffffu, wbytes, o);
+            }
+            const int my_pair = 2 * p + ((lane & 3) >> 1);
+            decode(i, it, my_pair);
+            const uint8_t *my_src = (lane < 4) ? ((lane & 1) ? ((it.a != nullptr) ? it.b : nullptr) : it.a) : nullptr;
+            const uint32_t my_dst = my_pair * kStageBytes + (lane & 1) * kChunkMaxBytes;
             for (int pc = 0; pc < P.nchunk; ++pc, ++q) {
-                const int chunk = pc;
                 const int first = it.row0, nr = it.nrows;
                 const uint32_t stage = q % kBlkStages;
                 if (q >= kBlkStages) {
@@ -279,20 +313,20 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
                 const uint32_t bar = full_b + stage * 8;
                 const uint32_t dst = smem_u + stage * kBlkStageBytes;
                 if (lane == 0) {
-                    if (pc == 0) queue[n % kBlkQueue] = i;  // read by the consumers once this stage is full
                     fence_proxy_async();
-                    mbar_expect_tx(bar, wbytes + nr * (kXqChunkRowBytes + kChunkBlocks * 4));
+                    // (copies of the other producers may land before this count is set: the phase cannot
+                    // complete before this arrival)
+                    if (p == 0) mbar_expect_tx(bar, wbytes + nr * (kXqChunkRowBytes + kChunkBlocks * 4));
                 }
                 __syncwarp();
-                const size_t off = (size_t)chunk * CHUNK_BYTES;
-                const long long cr = (long long)chunk * P.pcap + first;
-                if (lane < kBlkW) {
-                    if (it.a) bulk_g2s(dst + lane * kStageBytes, it.a + off, CHUNK_BYTES, bar);
-                    if (it.a && it.b) bulk_g2s(dst + lane * kStageBytes + kChunkMaxBytes, it.b + off, CHUNK_BYTES, bar);
-                } else if (lane == kBlkW) {
-                    bulk_g2s(dst + kBlkXOff, P.xq + cr * kXqChunkRowBytes, nr * kXqChunkRowBytes, bar);
-                } else if (lane == kBlkW + 1) {
-                    bulk_g2s(dst + kBlkCsOff, P.csum + cr * kChunkBlocks, nr * kChunkBlocks * 4, bar);
+                const size_t off = (size_t)pc * CHUNK_BYTES;
+                if (my_src) bulk_g2s(dst + my_dst, my_src + off, CHUNK_BYTES, bar);
+                if (p == 0) {
+                    const long long cr = (long long)pc * P.pcap + first;
+                    if (lane == 4)
+                        bulk_g2s(dst + kBlkXOff, P.xq + cr * kXqChunkRowBytes, nr * kXqChunkRowBytes, bar);
+                    else if (lane == 5)
+                        bulk_g2s(dst + kBlkCsOff, P.csum + cr * kChunkBlocks, nr * kChunkBlocks * 4, bar);
                 }
             }
         }

@@ -84,8 +84,8 @@ struct EpSelectArgs {
     unsigned epoch;
 };
 
-__global__ void __launch_bounds__(512) ep_select_scatter_kernel(const EpSelectArgs A) {
-    extern __shared__ __align__(16) unsigned char es_smem[];
+// (a device routine so that the routing launch's last chain CTA can run it without a launch of its own)
+__device__ __forceinline__ void ep_select_scatter_body(const EpSelectArgs &A, unsigned char *es_smem) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
     float *sig = reinterpret_cast<float *>(es_smem) + warp * 2 * A.E;
     unsigned *key = reinterpret_cast<unsigned *>(sig + A.E);
@@ -148,6 +148,25 @@ __global__ void __launch_bounds__(512) ep_select_scatter_kernel(const EpSelectAr
     if ((int)threadIdx.x < A.world)
         ep_st_release_sys(reinterpret_cast<unsigned *>(A.peers.base[threadIdx.x] + A.set_off + A.lay.ix_flag) + A.rank,
                           A.epoch);
+}
+
+__global__ void __launch_bounds__(512) ep_select_scatter_kernel(const EpSelectArgs A) {
+    extern __shared__ __align__(16) unsigned char es_smem[];
+    ep_select_scatter_body(A, es_smem);
+}
+
+// Routing launch of an expert-parallel rank: the exact chains and int8 rows of the home tokens
+// (route_fused_kernel without a plan); the chain CTA that finishes last selects and publishes the picks.
+__global__ void __launch_bounds__(kRtThreads, 1) route_fused_ep_kernel(const RouteArgs A, const EpSelectArgs S) {
+    extern __shared__ __align__(128) unsigned char rt_smem[];
+    if ((int)blockIdx.x >= A.n_chain_ctas) {
+        route_quantise_row(A, blockIdx.x - A.n_chain_ctas, rt_smem);
+        return;
+    }
+    if (route_chain_role(A, rt_smem, blockIdx.x)) {  // uniform over the CTA: this one saw all logits written
+        __syncthreads();
+        ep_select_scatter_body(S, rt_smem);
+    }
 }
 
 // ---- 2a. batch-wide plan once every rank's picks are here (one CTA).

@@ -166,7 +166,7 @@ def test_device_pointer_forward_matches_host_forward(dev):
 def test_speculative_routing_modes_agree_bit_for_bit(dev, m):
     # mode 0: exact chains first; 1: speculative pick checked against the exact chains;
     # 2: the speculative pick is forced wrong, so the recompute path produces the result
-    layer = synth_layer(300 + m, hidden=512, inter=160, n_experts=40, k=4, gs=32)
+    layer = synth_layer(300 + m, hidden=512, inter=256, n_experts=40, k=4, gs=32)
     x = synth_tokens(9 + m, m, 512)
     want, idx, w, keff, uni = oracle_layer_forward(layer, x, threads=4, want_routing=True)
     ml = upload_layer(dev, layer)
@@ -201,7 +201,8 @@ def test_blocking_single_token_calls_replay_a_graph(dev):
 
     if os.environ.get("PEREGRINE_B200_FORWARD_GRAPH") == "0" or os.environ.get("PEREGRINE_B200_FUSED_DECODE") == "0":
         pytest.skip("graph replay of the blocking call is switched off")
-    layer = synth_layer(77, hidden=512, inter=160, n_experts=40, k=4, gs=32)
+    # (the single-launch step wants hidden and inter in whole 256-element chunks)
+    layer = synth_layer(77, hidden=512, inter=256, n_experts=40, k=4, gs=32)
     xs = synth_tokens(78, 7, 512)
     wants = [oracle_layer_forward(layer, xs[i:i + 1], threads=4, want_routing=True) for i in range(7)]
     ml = upload_layer(dev, layer)
