@@ -125,7 +125,6 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
     int *cum = reinterpret_cast<int *>(smem + kBlkCumOff);
 
     const int n_slots = min(*P.n_slots, kBlkMaxSlots);
-    const int n_tb = (P.warp_tiles + kBlkW - 1) / kBlkW;
     // Work is cut into units (slot, block of `rpp` rows) times tile blocks; rpp = 32 unless the launch
     // asks for 16 or 8 (P.blk_rpp).  Smaller row blocks let several CTAs share the tensor-core and fold
     // work of an expert with many rows at the price of streaming its weights once per block; measured on
@@ -135,7 +134,7 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
     // counter: a CTA takes the next number when it has room in its ring, whatever the others hold.
     int *nrow_s = cum;                      // [n_slots] row counts
     int *units = reinterpret_cast<int *>(smem + kBlkUnitOff);   // [n_units] slot | first row << 16
-    __shared__ int s_rpp, s_nfull, s_units;
+    __shared__ int s_rpp, s_nfull, s_units, s_tbw;
     for (int s = tid; s < n_slots; s += blockDim.x) nrow_s[s] = P.slots[s].nrows;
     if (tid == 0) {
         for (int s = 0; s < kBlkStages; ++s) {
@@ -181,6 +180,17 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
         if (lane == 0) {
             s_rpp = rpp;
             s_nfull = min(base, kBlkMaxUnits);
+            // Tile pairs per item: 8 (all 16 consumer warps) unless the launch then has items for less
+            // than half (a quarter) of the CTAs: with 4 (2) pairs per item twice (four times) as many
+            // SMs share the work and no weight byte is fetched twice.  Not earlier: the consumer warps
+            // are bound by their own instruction latencies, so an SM's rate falls with the warps it runs
+            // (an expert-parallel rank with 112 items ran 10 % longer when they were cut into 224).
+            const int units_n = (rpp == 8) ? u8 : (rpp == 16 ? u16 : u32);
+            const int items8 = units_n * ((P.warp_tiles + 7) / 8);
+            int tbw = kBlkW;
+            if (2 * items8 <= (int)gridDim.x) tbw = 4;
+            if (4 * items8 <= (int)gridDim.x) tbw = 2;
+            s_tbw = tbw;
         }
     }
     __syncthreads();
@@ -205,24 +215,31 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
         }
     }
     __syncthreads();
-    const int rpp = s_rpp;
-    const int total = s_units * n_tb;
+    // (rows per unit, pairs per item and the item count stay in shared memory: they are needed once per
+    // item, and the consumers' inner loop has no register to spare for them)
+    __shared__ int s_ntb, s_total;
+    if (tid == 0) {
+        s_ntb = (P.warp_tiles + s_tbw - 1) / s_tbw;
+        s_total = s_units * s_ntb;
+    }
+    __syncthreads();
 
     volatile int *queue = reinterpret_cast<volatile int *>(smem + kBlkQueueOff);
     auto decode = [&](int i, BlkItem &it, int w) {
+        const int n_tb = s_ntb, tbw = s_tbw;
         const int u = i / n_tb;
         const int unit = units[u];
         const int slot = unit & 0xffff, r0 = unit >> 16;
         const GemvSlot *s = P.slots + slot;
         it.slot = slot;
         it.tb = i - u * n_tb;
-        it.nrows = min(rpp, s->nrows - r0);
+        it.nrows = min(s_rpp, s->nrows - r0);
         it.row0 = s->row0 + r0;
-        it.tile = it.tb * kBlkW + w;
+        it.tile = it.tb * tbw + w;
         it.a = it.b = nullptr;
         it.a_rs = s->a_rs;
         it.b_rs = s->b_rs;
-        if (it.tile < P.warp_tiles) {
+        if (w < tbw && it.tile < P.warp_tiles) {
             if (P.mode == 0) {
                 it.a = s->a + (unsigned long long)it.tile * P.tile_bytes;
                 it.b = s->b + (unsigned long long)it.tile * P.tile_bytes;
@@ -250,7 +267,7 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
             if (p == 0) {
                 if (lane == 0) {
                     i = (int)atomicAdd(&g_blk_dyn[0], 1u);
-                    if (i >= total) i = -1;
+                    if (i >= s_total) i = -1;
                     queue[n % kBlkQueue] = i;  // the consumers read it once the item's first stage is full
                     __threadfence_block();
                     *item_seq = n + 1;
