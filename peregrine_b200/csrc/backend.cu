@@ -565,7 +565,7 @@ static int block_launch(Ctx *c, const GemvParams &P0, bool grouped, int bpg) {
         return e ? std::atoi(e) : 0;
     }();
     GemvParams P = P0;
-    P.blk_rpp = rpp_env;  // 0: 32 rows per work unit
+    P.blk_rpp = rpp_env;  // 0: the kernel chooses
     if (!grouped) return block_launch_t<false, 1>(c, P);
     switch (bpg) {
         case 1: return block_launch_t<true, 1>(c, P);

@@ -279,7 +279,7 @@ struct GemvParams {
     int grid;  // host only: CTAs to launch (0 = one per SM)
     int pdl;   // host only: launch with programmatic stream serialisation (see griddep_wait)
     int tile_rb;  // host only: > 0 selects the large-batch tile kernel with this many row blocks in the grid
-    int blk_rpp;  // shared-row kernel: rows per work unit (16 or 8; anything else: 32)
+    int blk_rpp;  // shared-row kernel: rows per work unit (32, 16 or 8); 0: chosen by the kernel
     int umma;     // host only: with tile_rb > 0, take the tcgen05 kernel (activations in core-matrix order)
     const int *n_xrows_dev;     // rows actually valid (device scalar; nullptr: n_xrows)
     unsigned *amax_out;   // mode 0: per pair row, atomicMax of |h| bits (nullptr: off)

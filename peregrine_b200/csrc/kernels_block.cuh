@@ -125,11 +125,11 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
     int *cum = reinterpret_cast<int *>(smem + kBlkCumOff);
 
     const int n_slots = min(*P.n_slots, kBlkMaxSlots);
-    // Work is cut into units (slot, block of `rpp` rows) times tile blocks; rpp = 32 unless the launch
-    // asks for 16 or 8 (P.blk_rpp).  Smaller row blocks let several CTAs share the tensor-core and fold
-    // work of an expert with many rows at the price of streaming its weights once per block; measured on
-    // launches with few experts (an expert-parallel rank) that price was the higher one (experts phase
-    // 151 us at 32 rows per unit, 162 at 16, 186 at 8), so 32 is what the host passes.  Units are numbered
+    // Work is cut into units (slot, block of `rpp` rows) times tile blocks.  Smaller row blocks let several
+    // CTAs share the tensor-core and fold work of an expert with many rows at the price of streaming its
+    // weights once per block; whenever that made some CTA take a second item it cost more than it saved
+    // (an expert-parallel rank with 7 experts: experts phase 151 us at 32 rows per unit, 162 at 16, 186 at
+    // 8), so rpp is 32 unless every item of the finer cut still gets a CTA to itself.  Units are numbered
     // heaviest first (full units, then the ragged ends by falling row count) and handed out through a
     // counter: a CTA takes the next number when it has room in its ring, whatever the others hold.
     int *nrow_s = cum;                      // [n_slots] row counts
@@ -160,7 +160,17 @@ __global__ void __launch_bounds__(kBlkThreads, 1) gemv_w4a8_block_kernel(const G
             u16 += __shfl_xor_sync(0xffffffffu, u16, o);
             u8 += __shfl_xor_sync(0xffffffffu, u8, o);
         }
-        int rpp = (P.blk_rpp == 8 || P.blk_rpp == 16) ? P.blk_rpp : 32;
+        // rows per unit: 32, unless the launch is so small that even with 16 (8) rows per unit every item
+        // finds a CTA of its own at once: then the column groups of an expert with many rows run side by
+        // side instead of one after the other inside one CTA (its weights come from L2 for all but one)
+        int rpp = 32;
+        if (P.blk_rpp == 8 || P.blk_rpp == 16 || P.blk_rpp == 32) {
+            rpp = P.blk_rpp;
+        } else {
+            const int ntb8 = (P.warp_tiles + 7) / 8;
+            if (u16 * ntb8 <= (int)gridDim.x) rpp = 16;
+            if (u8 * ntb8 <= (int)gridDim.x) rpp = 8;
+        }
         if (((rpp == 8) ? u8 : (rpp == 16 ? u16 : u32)) > kBlkMaxUnits) rpp = 32;  // (never at these batch sizes)
         // full units first, in slot order: an exclusive scan of nrows / rpp over the slots
         int base = 0;

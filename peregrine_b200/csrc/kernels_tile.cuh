@@ -216,19 +216,25 @@ __global__ void __launch_bounds__(kTileThreads, 1) ffn_w4a8_tile_kernel(const Ge
 #pragma unroll
     for (int s = 0; s < 8; ++s) n_wt += wsrc[s] ? 1 : 0;
 
-    auto issue = [&](int chunk) {
+    // A bulk copy holds the issuing warp for ~130 cycles, one copy after the other, so the ten copies
+    // of a stage are shared out: lane 0 of warp w issues weight tile w, warp 0 also sets the stage's
+    // byte count, warps 1 and 2 also fetch the activation rows and their block sums.  (Copies of the
+    // other warps may land before the count is set; the phase cannot complete before that arrival.)
+    const uint8_t *w_mine = nullptr;
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+        if (s == warp) w_mine = wsrc[s];
+    auto issue = [&](int chunk) {  // lane 0 of every warp
         const int stage = chunk % kTileStages;
         const uint32_t bar = bar_u32 + stage * 8;
         const uint32_t dst = smem_u32(smem + stage * kTileStageBytes);
         const long long cr = (long long)chunk * P.pcap + prow0;
-        mbar_expect_tx(bar, n_wt * CHUNK_BYTES + nr * (kXqChunkRowBytes + kChunkBlocks * 4));
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-            if (wsrc[s]) bulk_g2s(dst + s * kChunkMaxBytes, wsrc[s] + (size_t)chunk * CHUNK_BYTES, CHUNK_BYTES, bar);
-        bulk_g2s(dst + kTileXOff, P.xq + cr * kXqChunkRowBytes, nr * kXqChunkRowBytes, bar);
-        bulk_g2s(dst + kTileCsOff, P.csum + cr * kChunkBlocks, nr * kChunkBlocks * 4, bar);
+        if (warp == 0) mbar_expect_tx(bar, n_wt * CHUNK_BYTES + nr * (kXqChunkRowBytes + kChunkBlocks * 4));
+        if (w_mine) bulk_g2s(dst + warp * kChunkMaxBytes, w_mine + (size_t)chunk * CHUNK_BYTES, CHUNK_BYTES, bar);
+        if (warp == 1) bulk_g2s(dst + kTileXOff, P.xq + cr * kXqChunkRowBytes, nr * kXqChunkRowBytes, bar);
+        if (warp == 2) bulk_g2s(dst + kTileCsOff, P.csum + cr * kChunkBlocks, nr * kChunkBlocks * 4, bar);
     };
-    if (tid == 0)
+    if (lane == 0)
         for (int c = 0; c < kTileStages - 1 && c < P.nchunk; ++c) issue(c);
 
     // accumulators [half][m-tile][n-tile][slot]; slot i: row g + 8*(i>>1), column 2t + (i&1)
@@ -253,10 +259,11 @@ __global__ void __launch_bounds__(kTileThreads, 1) ffn_w4a8_tile_kernel(const Ge
     for (int chunk = 0; chunk < P.nchunk; ++chunk) {
         // every warp is past chunk - 1, so its stage may be refilled
         __syncthreads();
-        if (tid == 0 && chunk + kTileStages - 1 < P.nchunk) {
+        if (lane == 0 && chunk + kTileStages - 1 < P.nchunk) {
             fence_proxy_async();
             issue(chunk + kTileStages - 1);
         }
+        __syncwarp();
         const int stage = chunk % kTileStages;
         {
             const bool ok = mbar_wait_bounded(bar_u32 + stage * 8, (chunk / kTileStages) & 1u);
