@@ -59,3 +59,45 @@ def test_argmax_rules_on_device(dev):
     assert ids.download((4,), np.int32).tolist() == [1, 3, 0, 2]
     lo.free()
     ids.free()
+
+
+def test_speculative_rows_emit_exactly_what_greedy_would(dev):
+    """Three sequences speculating three tokens deep are twelve rows of one forward; with right and
+    deliberately wrong drafts mixed the emitted streams equal token-by-token greedy decoding
+    (the rule of crates/peregrine-model/src/model.rs:383-406, 4028-4116)."""
+    from peregrine_b200.speculative import stack_forward_rows, verify_drafts
+
+    st = synth_stack(5, hidden=256, inter=64, dense_inter=128, n_experts=8, k=2, n_layers=3, first_dense=1, vocab=64)
+    ds = DeviceStack(dev, st, batch=12, max_steps=40)
+    start = [3, 17, 40]
+    steps = 24
+    greedy = ds.decode(np.asarray(start + [0] * 9, np.int32), steps)[:, :3].T  # [3, steps]: tokens after `start`
+    forward_rows = stack_forward_rows(ds)
+    rng = np.random.default_rng(0)
+    emitted = [[] for _ in start]
+    nxt = [None] * 3
+    # round 0: plain greedy for the first token (nothing confirmed yet to speculate from)
+    first = forward_rows(np.asarray(start, np.int32))
+    for s in range(3):
+        nxt[s] = int(first[s])
+    rounds = 0
+    while min(len(e) for e in emitted) < steps - 4:
+        drafts = []
+        for s in range(3):
+            pos = len(emitted[s]) + 1            # index in `greedy` of the token after nxt[s]
+            true = [int(t) for t in greedy[s, pos:pos + 3]]
+            if rng.random() < 0.5 and true:      # corrupt one draft: everything from it on must be rejected
+                j = int(rng.integers(len(true)))
+                true[j] = (true[j] + 1) % 64
+            drafts.append(true)
+        out = verify_drafts(forward_rows, nxt, drafts, [len(e) for e in emitted])
+        for s, v in enumerate(out):
+            emitted[s].extend(v.tokens)
+            nxt[s] = v.next
+        rounds += 1
+    for s in range(3):
+        n = min(len(emitted[s]), steps)  # (the last round may run past the reference's length)
+        assert n >= steps - 4 and emitted[s][:n] == [int(t) for t in greedy[s, :n]], f"sequence {s}"
+    assert rounds < steps  # speculation did accept drafts: fewer forwards than tokens
+    assert cuda.last_device_error(dev) == 0
+    ds.free()
