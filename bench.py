@@ -526,8 +526,9 @@ def extras_one_gpu(torch, cuda, ml, stream, flush, zbias, dev):
         "value": STACK["batch"] * STACK["steps"] / secs, "unit": UNIT, "seconds": secs, "batch": STACK["batch"],
         "steps": STACK["steps"], "layers": "3 dense (width 12288) + 5 MoE (256 experts top-8 + shared), hidden 6144, "
                                            "embedding, final norm, int4 lm_head (vocab 4096), greedy argmax",
-        "distinct_ids": int(len(np.unique(ids))), "timing": "CUDA events around the 256 steps; every step streams "
-        "several GB of expert weights, far more than the L2 holds"}
+        "distinct_ids": int(len(np.unique(ids))), "step_graphs": bool(ds.graphs),
+        "timing": "CUDA events around the 256 steps (each a replay of the recorded step graph when step_graphs is "
+                  "true); every step streams several GB of expert weights, far more than the L2 holds"}
     ds.free()
     return extra
 
@@ -559,8 +560,7 @@ def stack_decode(torch, cuda, dev, st, ids0, ep=None, meet=None):
     if meet:
         meet()
     ds.start(ids0)
-    for t in range(4):  # warm-up steps (overwritten by the timed run)
-        ds.step(t)
+    ds.run(4)  # warm-up steps (overwritten by the timed run); on one GPU this also records the step graphs
     stream.synchronize()
     if meet:
         meet()
@@ -568,8 +568,7 @@ def stack_decode(torch, cuda, dev, st, ids0, ep=None, meet=None):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record(stream)
-        for t in range(s["steps"]):
-            ds.step(t)
+        ds.run(s["steps"])
         e1.record(stream)
     stream.synchronize()
     if cuda.last_device_error(dev) != 0:

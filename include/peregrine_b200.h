@@ -280,6 +280,9 @@ int coli_cuda_moe_layer_ep_forward_dev(ColiCudaMoeLayer *layer, ColiCudaEp *ep, 
 /* Host-side microseconds of coli_cuda_moe_layer_forward since the last reset, by part: staging copy of
  * x, enqueueing the upload, enqueueing the launches, waiting for the device, copying the result out. */
 int coli_cuda_moe_layer_host_times(ColiCudaMoeLayer *layer, double *us5, uint64_t *calls, int reset);
+/* coli_cuda_graph_launch (which waits for the stream, as the reference's does) without the wait. */
+int coli_cuda_graph_launch_async(ColiCudaGraph *g);
+
 int coli_cuda_moe_layer_set_profile(ColiCudaMoeLayer *layer, int enable);
 int coli_cuda_moe_layer_profile(ColiCudaMoeLayer *layer, double *stage_ms7, uint64_t *calls);
 

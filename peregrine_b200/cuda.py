@@ -43,7 +43,7 @@ SYMBOLS = [
     "coli_cuda_tensor_upload_grouped", "coli_cuda_moe_layer_create", "coli_cuda_moe_layer_set_expert",
     "coli_cuda_moe_layer_free", "coli_cuda_moe_layer_forward_dev", "coli_cuda_moe_layer_forward",
     "coli_cuda_moe_layer_last_routing", "coli_cuda_moe_layer_enable_taps", "coli_cuda_moe_layer_set_spec",
-    "coli_cuda_moe_layer_set_fused", "coli_cuda_int8_peak_probe", "coli_cuda_tensor_clone", "coli_cuda_moe_layer_set_bias", "coli_cuda_moe_layer_decode_timeline", "coli_cuda_moe_layer_host_times", "coli_cuda_moe_layer_last_pairs",
+    "coli_cuda_moe_layer_set_fused", "coli_cuda_int8_peak_probe", "coli_cuda_tensor_clone", "coli_cuda_moe_layer_set_bias", "coli_cuda_moe_layer_decode_timeline", "coli_cuda_moe_layer_host_times", "coli_cuda_graph_launch_async", "coli_cuda_moe_layer_last_pairs",
     "coli_cuda_moe_layer_read_taps", "coli_cuda_moe_layer_set_ep", "coli_cuda_ep_create",
     "coli_cuda_ep_block_bytes", "coli_cuda_ep_local_base", "coli_cuda_ep_export", "coli_cuda_ep_attach",
     "coli_cuda_ep_attach_ptr", "coli_cuda_ep_free", "coli_cuda_ep_reset", "coli_cuda_moe_layer_ep_route_dev",
@@ -116,6 +116,7 @@ def lib():
         L.coli_cuda_graph_begin.argtypes = [i]
         L.coli_cuda_graph_end.argtypes = [i, vp]
         L.coli_cuda_graph_launch.argtypes = [vp]
+        L.coli_cuda_graph_launch_async.argtypes = [vp]
         L.coli_cuda_graph_free.argtypes = [vp]
         L.coli_cuda_graph_free.restype = None
         L.coli_cuda_moe_layer_create.argtypes = [vp, i, i, i, i, i, i, f, vp, vp]

@@ -10,6 +10,7 @@ the next step's embedding gather without a host round trip.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -113,6 +114,8 @@ class DeviceStack:
         self.u = _DevBuf(device, nbytes=b * widest * 4)
         self.logits = _DevBuf(device, nbytes=b * st.vocab * 4)
         self.ids = _DevBuf(device, nbytes=(max_steps + 1) * b * 4)
+        self.graphs = None  # step graphs: None = not tried yet, [] = not available
+        self.ping = self.pong = None
         self._L = L
 
     def _ok(self, rc, what):
@@ -120,11 +123,15 @@ class DeviceStack:
             raise cuda.CudaError(f"stack: {what} failed")
 
     def step(self, t: int):
-        """ids[t] -> ids[t+1], all on the device's stream."""
+        """ids[t] -> ids[t+1], all on the device's stream, one call per operation."""
+        b = self.batch
+        self._step_ops(self.ids.ptr + t * b * 4, self.ids.ptr + (t + 1) * b * 4)
+
+    def _step_ops(self, ids_in_ptr: int, ids_out_ptr: int):
         L, dev, st, b, d = self._L, self.device, self.st, self.batch, self.st.hidden
         vp = C.c_void_p
-        ids_in = vp(self.ids.ptr + t * b * 4)
-        ids_out = vp(self.ids.ptr + (t + 1) * b * 4)
+        ids_in = vp(ids_in_ptr)
+        ids_out = vp(ids_out_ptr)
         self._ok(L.coli_cuda_pipe_embed(dev, vp(self.x.ptr), vp(self.embed.ptr), ids_in, b, d, st.vocab), "embed")
         for li, layer in enumerate(self.layers):
             self._ok(L.coli_cuda_pipe_rmsnorm(dev, vp(self.nrm.ptr), vp(self.x.ptr), vp(self.norms[li].ptr), b, d,
@@ -155,16 +162,75 @@ class DeviceStack:
     def result(self, steps: int) -> np.ndarray:
         return self.ids.download((steps + 1, self.batch), np.int32)[1:]
 
-    def decode(self, ids0: np.ndarray, steps: int) -> np.ndarray:
-        """Greedy decode: returns int32 ids [steps, batch] (the tokens picked at each step)."""
+    def _record_step_graphs(self) -> bool:
+        """Records one decode step twice as a replayable graph (ids: ping -> pong and pong -> ping), in
+        the manner of the reference's COLI_CUDA_GRAPH pipe capture (cuda/backend_cuda.h:178-184): a step
+        is ~90 launches whose arguments never change, and enqueueing them one by one from the host takes
+        longer than the device needs to run them.  Needs one step already run (buffers sized, expert
+        tables uploaded).  Expert-parallel stacks keep the call-by-call path: their exchange numbers
+        its steps on the host."""
+        if self.ep is not None or os.environ.get("PEREGRINE_B200_STACK_GRAPH") == "0":
+            return False
+        L, dev, b = self._L, self.device, self.batch
+        self.ping = _DevBuf(dev, nbytes=b * 4)
+        self.pong = _DevBuf(dev, nbytes=b * 4)
+        graphs = []
+        for src, dst in ((self.ping, self.pong), (self.pong, self.ping)):
+            if L.coli_cuda_graph_begin(dev) != 1:
+                return False
+            try:
+                self._step_ops(src.ptr, dst.ptr)
+                ok = True
+            except cuda.CudaError:
+                ok = False
+            g = C.c_void_p()
+            if L.coli_cuda_graph_end(dev, C.byref(g)) != 1 or not ok:
+                for h in graphs:
+                    L.coli_cuda_graph_free(h)
+                return False
+            graphs.append(g)
+        self.graphs = graphs
+        return True
+
+    def run(self, steps: int):
+        """Enqueues `steps` greedy steps from ids[0] (see ``start``): ids[t + 1] = step(ids[t])."""
         if steps > self.max_steps:
             raise ValueError("more steps than the id buffer holds")
+        if steps < 1:
+            return
+        L, dev, b = self._L, self.device, self.batch
+        vp = C.c_void_p
+        if self.graphs is None:
+            self.step(0)  # call by call: sizes every buffer, uploads the expert tables
+            self.graphs = [] if not self._record_step_graphs() else self.graphs
+            first = 1
+        else:
+            first = 0
+        if not self.graphs:
+            for t in range(first, steps):
+                self.step(t)
+            return
+        row = lambda t: vp(self.ids.ptr + t * b * 4)
+        self._ok(L.coli_cuda_pipe_copy2d(dev, vp(self.ping.ptr), b, row(first), b, b, 1), "ids to the step graph")
+        bufs = (self.ping, self.pong)
+        for t in range(first, steps):
+            k = (t - first) & 1
+            self._ok(L.coli_cuda_graph_launch_async(self.graphs[k]), "step graph launch")
+            self._ok(L.coli_cuda_pipe_copy2d(dev, row(t + 1), b, vp(bufs[1 - k].ptr), b, b, 1), "ids of the step")
+
+    def decode(self, ids0: np.ndarray, steps: int) -> np.ndarray:
+        """Greedy decode: returns int32 ids [steps, batch] (the tokens picked at each step)."""
         self.start(ids0)
-        for t in range(steps):
-            self.step(t)
+        self.run(steps)
         return self.result(steps)
 
     def free(self):
+        for g in self.graphs or []:
+            self._L.coli_cuda_graph_free(g)
+        self.graphs = []
+        for buf in (self.ping, self.pong):
+            if buf is not None:
+                buf.free()
         for l in self.layers:
             l.free()
         self.lm_head.free()
