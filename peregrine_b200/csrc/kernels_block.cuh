@@ -5,15 +5,16 @@
 // rows alike; beyond 8 rows per expert the rows of a 256-element chunk (272 bytes each) weigh as much
 // as the chunk's packed weights (5 KB for a tile pair), the traffic from L2 into the SM doubles and
 // an expert with more than 16 rows is streamed once per 16 rows.  Here a work item is (expert, block
-// of up to 32 rows, block of 8 tile pairs): a producer warp fills a CTA-wide ring stage by stage with
-// the 8 pairs' weight chunks, ONE copy of the item's activation rows of that chunk and their block
+// of up to 32 rows, block of up to 8 tile pairs): four producer warps fill a CTA-wide ring stage by stage with
+// the pairs' weight chunks, ONE copy of the item's activation rows of that chunk and their block
 // sums; 16 consumer warps take one 16-row tile each (warp 2p + h: half h of pair p), multiply it with
 // all rows of the item (m16n8k32 int8 MMAs, 1 to 4 column groups of 8 rows, chosen per item) and fold
 // the group dots into fp32 in the reference's order (crates/peregrine-kernels/src/idot.rs:98-110,
 // matmul.rs:75-106): the same arithmetic, accumulator presets and packed fold as
 // gemv_w4a8_mma_kernel.  One tile per warp rather than a pair keeps four warps on every scheduler: a
 // chunk is a chain of shared-memory loads, MMAs and a sequential fold, and with two warps per
-// scheduler the issue slots stood empty two thirds of the time.  In a gate/up launch the up warp hands
+// scheduler the issue slots stood empty two thirds of the time (measured as fast as the pair version,
+// not faster: the SM's rate goes with the consumer warps it runs).  In a gate/up launch the up warp hands
 // its values to the gate warp of the pair through shared memory for the SwiGLU.  An expert's weights
 // are fetched once per 32 rows, the activation rows once per CTA instead of once per warp.  The
 // ordered combine is not fused here (at these batch sizes it is a launch of its own).
@@ -26,7 +27,7 @@ constexpr int kBlkW = 8;                  // tile pairs per work item
 constexpr int kBlkCW = 2 * kBlkW;         // consumer warps: one tile each
 constexpr int kBlkPW = 4;                 // producer warps: two tile pairs each (the first also the rows)
 constexpr int kBlkThreads = (kBlkCW + kBlkPW) * 32;
-constexpr int kBlkRows = 32;              // activation rows per pass
+constexpr int kBlkRows = 32;              // activation rows per work item, at most
 constexpr int kBlkStages = 4;
 constexpr int kBlkXOff = kBlkW * kStageBytes;
 constexpr int kBlkCsOff = kBlkXOff + kBlkRows * kXqChunkRowBytes;
